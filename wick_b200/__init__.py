@@ -16,9 +16,11 @@ from .config.base import (ConfigError, ModelConfig, architecture_names, config_f
 from .config.nibotar import NibotarConfig
 from .config.qwen3 import Qwen3Config
 from .config.tuguvik import TuguvikConfig
+from .config.fasunex import FasunexConfig
 from .models import qwen3 as _qwen3  # registers the architecture  # noqa: F401
 from .models import nibotar as _nibotar  # noqa: F401
 from .models import tuguvik as _tuguvik  # noqa: F401
+from .models import fasunex as _fasunex  # noqa: F401
 from .models.model import Model
 from .models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .sampling.sampler import Rng, Sampler, SamplerConfig
@@ -37,7 +39,7 @@ def __getattr__(name):
     raise AttributeError(name)
 
 
-__all__ = ["Architecture", "ConfigError", "Engine", "GenOptions", "GenResult", "LayerSpec", "Model", "ModelConfig",
+__all__ = ["Architecture", "ConfigError", "Engine", "FasunexConfig", "GenOptions", "GenResult", "LayerSpec", "Model", "ModelConfig",
            "ModelSpec", "NibotarConfig", "PartSpec", "Qwen3Config", "Rng", "SafeTensorsDir", "SafeTensorsError", "Sampler",
            "SamplerConfig", "ScheduleEntry", "TuguvikConfig", "WeightError", "architecture_names", "config_from_json", "generate",
            "get_architecture", "load_config", "load_weights", "register_architecture", "write_random_model",

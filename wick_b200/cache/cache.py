@@ -214,19 +214,27 @@ class Cache:
         self.slots = IndexPool(self.max_seqs + 1, reserved=(0,), what="slot")
         self.seqs: Dict[int, SeqRecord] = {}
         self.groups: List[_Group] = []
-        self.entry_place: Dict[int, Tuple[_Group, int]] = {}
+        # entry -> (group, index in the group), or a list of such for an entry that keeps several things
+        self.entry_place: Dict[int, object] = {}
         by_key: Dict[tuple, _Group] = {}
-        for i, need in enumerate(needs):
-            if need is None:
-                continue
+
+        def place(i: int, need: CacheNeed) -> Tuple[_Group, int]:
             if need.kind not in _STORAGE:
                 raise ValueError(f"unknown cache need {need.kind} (registered: {', '.join(sorted(_STORAGE))})")
             g = _Group(need, dtype)
             g = by_key.setdefault(g.key(), g)
             if not g.entries:
                 self.groups.append(g)
-            self.entry_place[i] = (g, len(g.entries))
             g.entries.append(i)
+            return g, len(g.entries) - 1
+
+        for i, need in enumerate(needs):
+            if need is None:
+                continue
+            if need.kind == "several":
+                self.entry_place[i] = [None if sub is None else place(i, sub) for sub in need.parts]
+            else:
+                self.entry_place[i] = place(i, need)
         for g in self.groups:
             g.store = _STORAGE[g.need.kind](g.need, len(g.entries), n_pages=self.n_pages, n_slots=self.max_seqs + 1,
                                             dtype=g.dtype, device=self.device)
@@ -294,6 +302,12 @@ class Cache:
         rec = self._rec(slot)
         if not 0 <= length <= rec.length:
             raise ValueError(f"cannot truncate slot {slot} of length {rec.length} to {length}")
+        if length < rec.length and any(isinstance(g.store, StateRecords) for g in self.groups):
+            # (a record that every token changed cannot be taken back to an earlier position)
+            if length != 0:
+                raise ValueError(f"slot {slot} holds per-sequence state and cannot go back from {rec.length} to {length} tokens")
+            for g in self.groups:
+                g.store.open_seq(slot)
         keep = (length + PAGE - 1) // PAGE
         for p in rec.pages[keep:]:
             self.pages.free(p)
@@ -332,5 +346,7 @@ class Cache:
         place = self.entry_place.get(entry)
         if place is None:
             return None
+        if isinstance(place, list):
+            return CacheView(parts=[None if p is None else p[0].store.view(p[1], batch) for p in place])
         g, idx = place
         return g.store.view(idx, batch)

@@ -34,6 +34,12 @@ __device__ __forceinline__ int first_visible(int p, int mask, int size) {
 //   pairing 0: (2i, 2i + 1) rotate together; 1: (i, i + rot_dims / 2).
 //   maps: a q or k head of d numbers is `maps` vectors of d / maps, side by side, each of which is
 //   turned on its own (the first rot_dims elements of each); 1: the head is one vector.
+//   cols: numbers a token's row of partial sums holds (the projection may carry further columns behind
+//   q, k and v, an output gate's for instance, which this kernel leaves alone).
+//   flags: FINISH_KEYS_ARE_VALUES: the row holds no values; a head's value is its key as projected, before
+//   any norm or rotation (e = d).  FINISH_NORM_AFTER: the norm follows the rotation instead of preceding it.
+//   A span without a weight vector (q_span > 0, q_w null) is divided by its root mean square and no more.
+constexpr int FINISH_KEYS_ARE_VALUES = 1, FINISH_NORM_AFTER = 2;
 constexpr int MAX_SPANS = 512;                  // spans of the two norms together (a span per head at most)
 
 template <typename T>
@@ -43,7 +49,7 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
                   int k_span, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
                   int pairing, int maps, float* __restrict__ v_keep, int v_mode, const float* __restrict__ lambda, T* __restrict__ q_out,
                   T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
-                  const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
+                  const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv, int cols, int flags) {
     extern __shared__ float row[];
     __shared__ float partial[MAX_SPANS], span_scale[MAX_SPANS];
     pdl_trigger();
@@ -53,8 +59,9 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
     cos_t = fresh(cos_t);
     sin_t = fresh(sin_t);
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
-    const int Wq = H * d, Wk = G * d, Wv = G * e, W = Wq + Wk + Wv;
-    if ((W & 3) == 0 && (split_stride & 3) == 0) {
+    const bool keys_are_values = flags & FINISH_KEYS_ARE_VALUES, norm_after = flags & FINISH_NORM_AFTER;
+    const int Wq = H * d, Wk = G * d, Wv = G * e, W = Wq + Wk + (keys_are_values ? 0 : Wv);
+    if ((W & 3) == 0 && (cols & 3) == 0 && (split_stride & 3) == 0) {
         // four neighbours a load, the loads of four partial sums issued together (a chain of dependent trips to
         // the L2 cache is what a step of few tokens would otherwise wait for); the sums in index order
         for (int j = tid * 4; j < W; j += blockDim.x * 4) {
@@ -63,7 +70,7 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
                 float4 p4[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
-                    p4[u] = s0 + u < splits ? *reinterpret_cast<const float4*>(parts + (s0 + u) * split_stride + (int64_t)t * W + j)
+                    p4[u] = s0 + u < splits ? *reinterpret_cast<const float4*>(parts + (s0 + u) * split_stride + (int64_t)t * cols + j)
                                             : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -77,16 +84,49 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
         }
     } else {
         for (int j = tid; j < W; j += blockDim.x) {
-            float v = parts[(int64_t)t * W + j];
-            for (int s = 1; s < splits; ++s) v += parts[s * split_stride + (int64_t)t * W + j];
+            float v = parts[(int64_t)t * cols + j];
+            for (int s = 1; s < splits; ++s) v += parts[s * split_stride + (int64_t)t * cols + j];
             if (bias) v += bias[j];
             row[j] = v;
         }
     }
     __syncthreads();
+    const int pos = positions[t];
+    const float lam = v_mode == 2 ? *lambda : 0.f;
+    T* page = nullptr;
+    if (write_kv) {
+        const int pg = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
+        page = kv + (int64_t)pg * G * kPage * (d + e);
+    }
+    const int r = pos % kPage;
+    const int half = cos_t ? rot_dims >> 1 : 0, rot = 2 * half;
+    const int dm = d / maps;                               // a vector that turns on its own (the whole head, or one of its maps)
+    // The values first (they read the row as projected): blended where asked, then stored.
+    for (int j = tid; j < Wv; j += blockDim.x) {
+        float v = row[(keys_are_values ? Wq : Wq + Wk) + j];
+        if (v_mode == 1) v_keep[(int64_t)t * Wv + j] = v;
+        if (v_mode == 2) v = (1.0f - lam) * v + lam * v_keep[(int64_t)t * Wv + j];
+        if (write_kv) {
+            const int g = j / e, x = j - g * e;
+            st(page + (int64_t)G * kPage * d + ((int64_t)g * kPage + r) * e + x, v);
+        }
+    }
+    if (norm_after && half > 0) {
+        // the rotation comes before the norm: the pairs turn in place, and the pass at the end turns nothing
+        __syncthreads();
+        for (int idx = tid; idx < (H + G) * maps * half; idx += blockDim.x) {
+            const int h = idx / half, i = idx - h * half;
+            const int j0 = pairing == 0 ? 2 * i : i, j1 = pairing == 0 ? 2 * i + 1 : i + half;
+            const float u = row[h * dm + j0], v = row[h * dm + j1];
+            const float cs = cos_t[(int64_t)t * half + i], sn = sin_t[(int64_t)t * half + i];
+            row[h * dm + j0] = u * cs - v * sn;
+            row[h * dm + j1] = v * cs + u * sn;
+        }
+        __syncthreads();
+    }
     // The norms: every span's sum of squares is made by `per` warps (each a slice of the span: lane l its
     // elements l, l + 32, ...; the 32 sums by the butterfly), the slices' sums are added in index order.
-    const int nq = q_w ? Wq / q_span : 0, nk = k_w ? Wk / k_span : 0, n_spans = nq + nk;
+    const int nq = q_span > 0 ? Wq / q_span : 0, nk = k_span > 0 ? Wk / k_span : 0, n_spans = nq + nk;
     if (n_spans > 0) {
         const int per = max(1, n_warps / n_spans);
         for (int unit = warp; unit < n_spans * per; unit += n_warps) {
@@ -110,16 +150,6 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
     }
     // One pass over the pairs of every q and k head: the norm's factor and weight, the rotation (pairs of the first
     // rot_dims elements; the others pass), and the store.  Nothing goes back to shared memory.
-    const int pos = positions[t];
-    const float lam = v_mode == 2 ? *lambda : 0.f;
-    T* page = nullptr;
-    if (write_kv) {
-        const int pg = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
-        page = kv + (int64_t)pg * G * kPage * (d + e);
-    }
-    const int r = pos % kPage;
-    const int half = cos_t ? rot_dims >> 1 : 0, rot = 2 * half;
-    const int dm = d / maps;                               // a vector that turns on its own (the whole head, or one of its maps)
     const int pairs = half + (dm - rot + 1) / 2;           // per vector: the turning pairs, then neighbours of the rest
     for (int idx = tid; idx < (H + G) * maps * pairs; idx += blockDim.x) {
         const int h = idx / pairs, i = idx - h * pairs;     // h counts the vectors: q's, then k's
@@ -135,14 +165,17 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
         const int base = h * dm;                            // (the k vectors follow the q vectors at the same stride)
         float u = row[base + j0], v = two ? row[base + j1] : 0.f;
         const float* w = is_q ? q_w : k_w;
-        if (w) {
-            const int span = is_q ? q_span : k_span;
+        const int span = is_q ? q_span : k_span;
+        if (span > 0) {
             const int o0 = (is_q ? base : base - Wq) + j0, o1 = (is_q ? base : base - Wq) + j1;   // index inside the projection
-            const float sc0 = span_scale[(is_q ? 0 : nq) + o0 / span];
-            u = (u * sc0) * w[o0 % span];
-            if (two) v = (v * span_scale[(is_q ? 0 : nq) + o1 / span]) * w[o1 % span];
+            u *= span_scale[(is_q ? 0 : nq) + o0 / span];
+            if (two) v *= span_scale[(is_q ? 0 : nq) + o1 / span];
+            if (w) {
+                u *= w[o0 % span];
+                if (two) v *= w[o1 % span];
+            }
         }
-        if (i < half) {
+        if (i < half && !norm_after) {
             const float cs = cos_t[(int64_t)t * half + i], sn = sin_t[(int64_t)t * half + i];
             const float ru = u * cs - v * sn, rv = v * cs + u * sn;
             u = ru;
@@ -157,15 +190,6 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
             T* o = page + ((int64_t)kh * kPage + r) * d + km * dm;
             st(o + j0, u);
             if (two) st(o + j1, v);
-        }
-    }
-    for (int j = tid; j < Wv; j += blockDim.x) {
-        float v = row[Wq + Wk + j];
-        if (v_mode == 1) v_keep[(int64_t)t * Wv + j] = v;
-        if (v_mode == 2) v = (1.0f - lam) * v + lam * v_keep[(int64_t)t * Wv + j];
-        if (write_kv) {
-            const int g = j / e, x = j - g * e;
-            st(page + (int64_t)G * kPage * d + ((int64_t)g * kPage + r) * e + x, v);
         }
     }
 }
@@ -497,16 +521,18 @@ template <typename T>
 int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,
                int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t, int rot_dims,
                int pairing, int maps, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table,
-               int table_width, const int* seq_of_token, const int* positions, int write_kv, cudaStream_t s) {
+               int table_width, const int* seq_of_token, const int* positions, int write_kv, int cols, int flags, cudaStream_t s) {
     WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "qkv_finish: bad head counts or sizes");
+    WICK_REQUIRE(!(flags & FINISH_KEYS_ARE_VALUES) || (d == e && v_mode == 0), "qkv_finish: keys that are values have the values' size and are not blended");
+    WICK_REQUIRE(cols >= H * d + G * d + ((flags & FINISH_KEYS_ARE_VALUES) ? 0 : G * e), "qkv_finish: rows of %d numbers are too short", cols);
     WICK_REQUIRE(maps >= 1 && d % maps == 0, "qkv_finish: a head of %d numbers is not %d vectors", d, maps);
     WICK_REQUIRE(splits >= 1, "qkv_finish: partial sums are needed");
     const int Wq = H * d, Wk = G * d;
-    if (q_w) WICK_REQUIRE(q_span > 0 && Wq % q_span == 0, "qkv_finish: a q norm span of %d does not divide %d", q_span, Wq);
-    if (k_w) WICK_REQUIRE(k_span > 0 && Wk % k_span == 0, "qkv_finish: a k norm span of %d does not divide %d", k_span, Wk);
+    if (q_w || q_span) WICK_REQUIRE(q_span > 0 && Wq % q_span == 0, "qkv_finish: a q norm span of %d does not divide %d", q_span, Wq);
+    if (k_w || k_span) WICK_REQUIRE(k_span > 0 && Wk % k_span == 0, "qkv_finish: a k norm span of %d does not divide %d", k_span, Wk);
     WICK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d / maps, "qkv_finish: %d rotated dims of %d", rot_dims, d / maps);
     WICK_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qkv_finish: the two angle tables come together");
-    WICK_REQUIRE((q_w ? Wq / q_span : 0) + (k_w ? Wk / k_span : 0) <= MAX_SPANS, "qkv_finish: too many norm spans");
+    WICK_REQUIRE((q_span ? Wq / q_span : 0) + (k_span ? Wk / k_span : 0) <= MAX_SPANS, "qkv_finish: too many norm spans");
     WICK_REQUIRE(v_mode == 0 || v_keep, "qkv_finish: the kept values are missing");
     WICK_REQUIRE(v_mode != 2 || lambda, "qkv_finish: the blend factor is missing");
     if (n == 0) return 0;
@@ -517,9 +543,9 @@ int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, 
         WICK_CUDA(cudaFuncSetAttribute(qkv_finish_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         raised = true;
     }
-    WICK_CUDA(launch(qkv_finish_kernel<T>, dim3(n), dim3(256), smem, s, parts, splits, (int64_t)n * (Wq + Wk + G * e), bias, H, G,
+    WICK_CUDA(launch(qkv_finish_kernel<T>, dim3(n), dim3(256), smem, s, parts, splits, (int64_t)n * cols, bias, H, G,
                      d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing, maps, v_keep, v_mode, lambda, (T*)q_out,
-                     (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
+                     (T*)kv, page_table, table_width, seq_of_token, positions, write_kv, cols, flags));
     return check_launch("qkv_finish");
 }
 
@@ -569,10 +595,10 @@ typedef __nv_bfloat16 bf16;
                       int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t,               \
                       int rot_dims, int pairing, int maps, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, \
                       const int* page_table, int table_width, const int* seq_of_token, const int* positions, int write_kv,       \
-                      void* s) {                                                                                                 \
+                      int cols, int flags, void* s) {                                                                            \
         return qkv_finish<T>(parts, splits, n, bias, H, G, d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing,  \
                              maps, v_keep, v_mode, lambda, q_out, kv, page_table, table_width, seq_of_token, positions, write_kv,      \
-                             (cudaStream_t)s);                                                                                   \
+                             cols, flags, (cudaStream_t)s);                                                                      \
     }
 WICK_QKV_FINISH(wick_qkv_finish_bf16, bf16)
 WICK_QKV_FINISH(wick_qkv_finish_f32, float)

@@ -225,6 +225,64 @@ __global__ void gelu_gate_rows_kernel(const float* __restrict__ z, const T* __re
     st(out + i, g * ld(table + (int64_t)tokens[t] * row_width + offset + j));
 }
 
+
+// y[t, j] <- y[t, j] * sigmoid(g[t, j]), g the sum of the partial sums at column first_col + j of a token's row of `cols`
+// numbers (an output gate that came out of the same product as the projections it gates).  float32 arithmetic.
+template <typename T>
+__global__ void gate_rows_kernel(T* __restrict__ y, const float* __restrict__ parts, int splits, int64_t split_stride, int64_t n,
+                                 int width, int cols, int first_col) {
+    pdl_trigger();
+    pdl_wait();
+    y = fresh(y);
+    parts = fresh(parts);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * width) return;
+    const int64_t t = i / width;
+    const int j = (int)(i - t * width);
+    float g = 0.f;
+    for (int s = 0; s < splits; ++s) g += parts[s * split_stride + t * cols + first_col + j];
+    st(y + i, ld(y + i) / (1.0f + expf(-g)));
+}
+
+// out = f_0 sum(a_0) + f_1 sum(a_1) + ...: up to four terms of partial sums (each added in index order), the terms
+// in the order given.
+struct SumTerms {
+    const float* a[4];
+    int splits[4];
+    float f[4];
+};
+__global__ void weighted_sum_kernel(SumTerms terms, float* __restrict__ out, int64_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (terms.a[k] == nullptr) continue;
+        const float* a = fresh(terms.a[k]);
+        float sum = 0.f;
+        for (int s = 0; s < terms.splits[k]; ++s) sum += a[s * n + i];
+        v = k == 0 ? terms.f[k] * sum : fmaf(terms.f[k], sum, v);
+    }
+    out[i] = v;
+}
+
+// out[t] = [a[t] | b[t]] in the activation type.
+template <typename T>
+__global__ void concat_activation_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int64_t n,
+                                         int wa, int wb) {
+    pdl_trigger();
+    pdl_wait();
+    a = fresh(a);
+    b = fresh(b);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * (wa + wb)) return;
+    const int64_t t = i / (wa + wb);
+    const int j = (int)(i - t * (wa + wb));
+    st(out + i, j < wa ? a[t * wa + j] : b[t * wb + (j - wa)]);
+}
+
 template <typename TOut>
 int stream_update(float* x, const float* delta, int splits, const float* scale, const float* rms_w, float rms_eps,
                   const float* alpha, const float* w, const float* b, const int* rows, void* out, int n, int n_out, int width,
@@ -335,3 +393,35 @@ WICK_API int wick_to_activation_bf16(const float* x, void* out, int64_t n, void*
     WICK_CUDA(launch(to_activation_kernel<bf16>, dim3(ceil_div(n, 256)), dim3(256), 0, (cudaStream_t)s, x, (bf16*)out, n));
     return check_launch("to_activation");
 }
+
+// y: [n, width] in the activation type, gated in place; parts: float32 [splits, n, cols].
+#define WICK_GATE_ROWS(NAME, T)                                                                                              \
+    WICK_API int NAME(void* y, const float* parts, int splits, int n, int width, int cols, int first_col, void* s) {          \
+        WICK_REQUIRE(splits >= 1 && first_col >= 0 && first_col + width <= cols, "gate_rows: bad columns");                  \
+        if (n == 0 || width == 0) return 0;                                                                                  \
+        WICK_CUDA(launch(gate_rows_kernel<T>, dim3(ceil_div((int64_t)n * width, 256)), dim3(256), 0, (cudaStream_t)s, (T*)y,  \
+                         parts, splits, (int64_t)n * cols, (int64_t)n, width, cols, first_col));                              \
+        return check_launch("gate_rows");                                                                                    \
+    }
+WICK_GATE_ROWS(wick_gate_rows_bf16, bf16)
+WICK_GATE_ROWS(wick_gate_rows_f32, float)
+
+// a_k: float32 [splits_k, n] or null; out: float32 [n].
+WICK_API int wick_weighted_sum(const float* a0, int s0, float f0, const float* a1, int s1, float f1, const float* a2, int s2,
+                               float f2, const float* a3, int s3, float f3, float* out, int64_t n, void* s) {
+    WICK_REQUIRE(a0 != nullptr, "weighted_sum: the first term is missing");
+    if (n == 0) return 0;
+    SumTerms t = {{a0, a1, a2, a3}, {s0, s1, s2, s3}, {f0, f1, f2, f3}};
+    WICK_CUDA(launch(weighted_sum_kernel, dim3(ceil_div(n, 256)), dim3(256), 0, (cudaStream_t)s, t, out, n));
+    return check_launch("weighted_sum");
+}
+
+#define WICK_CONCAT_ACTIVATION(NAME, T)                                                                                      \
+    WICK_API int NAME(const float* a, const float* b, void* out, int n, int wa, int wb, void* s) {                            \
+        if (n == 0 || wa + wb == 0) return 0;                                                                                \
+        WICK_CUDA(launch(concat_activation_kernel<T>, dim3(ceil_div((int64_t)n * (wa + wb), 256)), dim3(256), 0,              \
+                         (cudaStream_t)s, a, b, (T*)out, (int64_t)n, wa, wb));                                                \
+        return check_launch("concat_activation");                                                                            \
+    }
+WICK_CONCAT_ACTIVATION(wick_concat_activation_bf16, bf16)
+WICK_CONCAT_ACTIVATION(wick_concat_activation_f32, float)

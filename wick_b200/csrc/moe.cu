@@ -315,6 +315,129 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     }
 }
 
+
+// ---- experts chosen by a router ---------------------------------------------------------------
+// One warp per token.  z = the router's logits (float32 partial sums, added in index order) over all its outputs;
+// s = softmax(z); the `top` outputs with the largest s + correction are chosen (the lowest index among equals),
+// one after the other; choice[t][c] = the output's index, weight[t][c] = s of it (divided by the chosen ones' sum
+// if `renormalize`).  Outputs from n_experts on stand for experts without matrices; the kernels that walk the
+// experts' matrices pass them over.  ident[t] = t: with it as "token ids", choice is the table those kernels read.
+__global__ void __launch_bounds__(32)
+moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int n_out, const float* __restrict__ correction,
+                  int top, int renormalize, int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ ident) {
+    extern __shared__ float sm[];
+    float* score = sm;                                                  // [n_out]
+    float* pick = sm + n_out;                                           // [n_out]: score + correction, -inf once chosen
+    pdl_trigger();
+    pdl_wait();
+    parts = fresh(parts);
+    const int t = blockIdx.x, lane = threadIdx.x;
+    float m = -INFINITY;
+    for (int e = lane; e < n_out; e += 32) {
+        float z = 0.f;
+        for (int s = 0; s < splits; ++s) z += parts[s * split_stride + (int64_t)t * n_out + e];
+        score[e] = z;
+        m = fmaxf(m, z);
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < n_out; e += 32) {
+        const float p = expf(score[e] - m);
+        score[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < n_out; e += 32) {
+        score[e] *= inv;
+        pick[e] = score[e] + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    float chosen_sum = 0.f;
+    for (int c = 0; c < top; ++c) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_out; e += 32)
+            if (pick[e] > best) {                                      // (a lane's candidates in index order: the first of equals stays)
+                best = pick[e];
+                at = e;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) {
+                best = ob;
+                at = oa;
+            }
+        }
+        if (at >= n_out) at = 0;                                        // (nothing left to choose: scores that are no numbers)
+        if (lane == 0) {
+            choice[(int64_t)t * top + c] = at;
+            weight[(int64_t)t * top + c] = score[at];
+            pick[at] = -INFINITY;
+        }
+        chosen_sum += score[at];
+        __syncwarp();
+    }
+    if (renormalize && lane == 0)
+        for (int c = 0; c < top; ++c) weight[(int64_t)t * top + c] /= chosen_sum;
+    if (lane == 0 && ident) ident[t] = t;
+}
+
+// y[pair][o] = down_{e(pair)}[o] . hidden[pair], every pair on its own.  grid (pairs, ceil(width / (warps x ROWS_PER_WARP))).
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_down_pair_kernel(const T* __restrict__ hidden, const int* __restrict__ tokens, const int* __restrict__ table, int top,
+                     int n_experts, const T* __restrict__ down, float* __restrict__ y, int width, int ff) {
+    extern __shared__ float hs[];                                       // [ff]
+    pdl_trigger();
+    pdl_wait();
+    hidden = fresh(hidden);
+    const int pair = blockIdx.x, t = pair / top, c = pair - t * top;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ex = table[(int64_t)tokens[t] * top + c];
+    if (ex < 0 || ex >= n_experts) return;
+    for (int j = threadIdx.x; j < ff; j += blockDim.x) hs[j] = ld(hidden + (int64_t)pair * ff + j);
+    __syncthreads();
+    const int o0 = (blockIdx.y * (blockDim.x >> 5) + warp) * ROWS_PER_WARP;
+    for (int o = o0; o < min(o0 + ROWS_PER_WARP, width); ++o) {
+        const float v = dot_row(down + ((int64_t)ex * width + o) * ff, hs, ff, lane);
+        if (lane == 0) y[(int64_t)pair * width + o] = v;
+    }
+}
+
+// out[t] = sum over c of weight[t][c] * r(t, c), choices in index order:  r = the row of y that holds the pair's result
+// (row_of[t][c], or the pair's own number where the rows are not sorted) for an expert with matrices; x[t] itself for
+// an output that stands for an expert that returns its input; nothing otherwise.
+template <typename T>
+__global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ row_of, const int* __restrict__ choice,
+                                            const float* __restrict__ weight, const T* __restrict__ x, int n_experts, int top,
+                                            float* __restrict__ out, int width) {
+    pdl_trigger();
+    pdl_wait();
+    y = fresh(y);
+    row_of = fresh(row_of);
+    choice = fresh(choice);
+    weight = fresh(weight);
+    x = fresh(x);
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float sum = 0.f;
+        for (int c = 0; c < top; ++c) {
+            const int ex = choice[(int64_t)t * top + c];
+            const float wgt = weight[(int64_t)t * top + c];
+            if (ex >= 0 && ex < n_experts) {
+                const int64_t row = row_of ? row_of[(int64_t)t * top + c] : (int64_t)t * top + c;
+                if (row >= 0) sum = fmaf(wgt, y[row * width + j], sum);
+            } else if (ex >= n_experts && x) {
+                sum = fmaf(wgt, ld(x + (int64_t)t * width + j), sum);
+            }
+        }
+        out[(int64_t)t * width + j] = sum;
+    }
+}
+
 template <typename T>
 int moe_up(const void* x, const int* tokens, const int* table, int top, int n_experts, const void* gate_up, void* hidden, int n,
            int width, int ff, cudaStream_t s) {
@@ -415,3 +538,55 @@ WICK_API int wick_moe_combine(const float* y, const int* row_of, int top, float 
                      (int64_t)n * width, out, width));
     return check_launch("moe_combine");
 }
+
+// parts: float32 [splits, n, n_out] (the router's logits as partial sums); correction: float32 [n_out] or null;
+// choice: int32 [n, top]; weight: float32 [n, top]; ident: int32 [n] or null.
+WICK_API int wick_moe_router(const float* parts, int splits, int n, int n_out, const float* correction, int top, int renormalize,
+                             int* choice, float* weight, int* ident, void* s) {
+    WICK_REQUIRE(splits >= 1 && n_out > 0 && top > 0 && top <= n_out, "moe_router: bad sizes");
+    WICK_REQUIRE((size_t)n_out * 8 <= 48 * 1024, "moe_router: %d outputs are beyond one block's shared memory", n_out);
+    if (n == 0) return 0;
+    WICK_CUDA(launch(moe_router_kernel, dim3(n), dim3(32), (size_t)n_out * 2 * sizeof(float), (cudaStream_t)s, parts, splits,
+                     (int64_t)n * n_out, n_out, correction, top, renormalize, choice, weight, ident));
+    return check_launch("moe_router");
+}
+
+// y: float32 [n * top, width], zero on entry where pairs without an expert must read as nothing.
+template <typename T>
+static int moe_expert_down(const void* hidden, const int* tokens, const int* table, int top, int n_experts, const void* down, float* y,
+                           int n, int width, int ff, cudaStream_t s) {
+    WICK_REQUIRE(top > 0 && n_experts > 0 && width > 0 && ff > 0, "moe_expert_down: bad sizes");
+    if (n == 0) return 0;
+    const int warps = 4;
+    if ((int64_t)n * top <= PAIRS_BY_EXPERT) {
+        WICK_CUDA(launch(moe_expert_rows_kernel<T, false>, dim3(n_experts, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32),
+                         (size_t)n * top * sizeof(int), s, (const T*)hidden, tokens, table, top, n * top, (const T*)down, (T*)nullptr,
+                         y, width, ff));
+        return check_launch("moe_expert_down");
+    }
+    WICK_REQUIRE((size_t)ff * 4 <= 48 * 1024, "moe_expert_down: an inner size of %d is beyond one block's shared memory", ff);
+    WICK_CUDA(launch(moe_down_pair_kernel<T>, dim3(n * top, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32), (size_t)ff * 4, s,
+                     (const T*)hidden, tokens, table, top, n_experts, (const T*)down, y, width, ff));
+    return check_launch("moe_expert_down");
+}
+WICK_API int wick_moe_expert_down_bf16(const void* hidden, const int* tokens, const int* table, int top, int n_experts,
+                                       const void* down, float* y, int n, int width, int ff, void* s) {
+    return moe_expert_down<bf16>(hidden, tokens, table, top, n_experts, down, y, n, width, ff, (cudaStream_t)s);
+}
+WICK_API int wick_moe_expert_down_f32(const void* hidden, const int* tokens, const int* table, int top, int n_experts,
+                                      const void* down, float* y, int n, int width, int ff, void* s) {
+    return moe_expert_down<float>(hidden, tokens, table, top, n_experts, down, y, n, width, ff, (cudaStream_t)s);
+}
+
+// y: float32 rows; row_of: int32 [n, top] or null (rows in pair order); choice: int32 [n, top]; weight: float32 [n, top];
+// x: [n, width] or null (what an expert without matrices returns); out: float32 [n, width].
+#define WICK_MOE_COMBINE_WEIGHTED(NAME, T)                                                                                    \
+    WICK_API int NAME(const float* y, const int* row_of, const int* choice, const float* weight, const void* x, int n_experts, \
+                      int top, float* out, int n, int width, void* s) {                                                       \
+        if (n == 0) return 0;                                                                                                 \
+        WICK_CUDA(launch(moe_combine_weighted_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)s, y, row_of, choice, weight,     \
+                         (const T*)x, n_experts, top, out, width));                                                            \
+        return check_launch("moe_combine_weighted");                                                                          \
+    }
+WICK_MOE_COMBINE_WEIGHTED(wick_moe_combine_weighted_bf16, bf16)
+WICK_MOE_COMBINE_WEIGHTED(wick_moe_combine_weighted_f32, float)

@@ -1,0 +1,286 @@
+// A selective state-space recurrence per head (the "state-space duality" form: one decay number per head and
+// token), with its short causal convolution, for steps of any shape over per-sequence state records.
+//
+// The input projection's float32 partial sums hold, per token, [z: inner | x: inner | B: G N | C: G N | dt: H],
+// inner = H P (H heads of P numbers), N the state size, G groups of heads that share B and C.
+//
+//   conv       : u = [x | B | C] (channels = inner + 2 G N);  c_t = silu(b + sum_k w[., k] u_(t - (K - 1) + k)), zeros
+//                before position 0; inputs of earlier steps come from the sequence's record
+//   conv state : the record's last K - 1 inputs are brought up to date
+//   scan       : dt_t = softplus(dt_t + dt_bias_h);  a_t = exp(-exp(A_log_h) dt_t);
+//                S_t = a_t S_(t-1) + dt_t B_t x_t^T  (N x P per head);  y_t = S_t^T C_t + D_h x_t
+//   gate, norm : g = y * silu(z);  `parts` equal runs of g are each divided by their own root mean square and
+//                multiplied by a weight; the result goes out in the activation type
+//
+// A sequence's record (float32): [K - 1][channels] inputs of the convolution, oldest first, then the state as
+// [H][P][N] (a column of S, the N numbers that meet one element of x, lies together).  Everything here is float32
+// arithmetic; a token's numbers depend on its own sequence alone and are added in the same order whatever the step's shape
+// (a prompt in one step, in several, or token by token).
+#include "common.cuh"
+
+namespace wick {
+
+constexpr int SSM_MAX_TAPS = 16;
+constexpr int SSM_ROWS = 16;                    // state numbers a thread keeps of one column, at most
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+__device__ __forceinline__ float sum_parts(const float* __restrict__ parts, int splits, int64_t split_stride, int64_t at) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += parts[s * split_stride + at];
+    return v;
+}
+
+// grid (tokens, ceil(channels / 256)).
+__global__ void __launch_bounds__(256)
+ssm_conv_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int cols, int first_col, int channels, int taps,
+                const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state, int64_t record,
+                const int* __restrict__ slots, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                const int* __restrict__ start, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    parts = fresh(parts);
+    state = fresh(state);
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int b = seq_of_token[t], pos = positions[t], first = start[b];
+    const float* rec = state + (int64_t)slots[b] * record;
+    float acc = bias ? bias[c] : 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int sp = pos - (taps - 1) + k;
+        float u = 0.f;
+        if (sp >= first) u = sum_parts(parts, splits, split_stride, (int64_t)(t - (pos - sp)) * cols + first_col + c);
+        else if (sp >= 0) u = rec[(int64_t)(sp - (first - (taps - 1))) * channels + c];
+        acc = fmaf(w[(int64_t)c * taps + k], u, acc);
+    }
+    out[(int64_t)t * channels + c] = silu_f(acc);
+}
+
+// grid (sequences, ceil(channels / 256)).  Runs after the convolution has read the old inputs.
+__global__ void __launch_bounds__(256)
+ssm_conv_state_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int cols, int first_col, int channels,
+                      int taps, float* __restrict__ state, int64_t record, const int* __restrict__ slots,
+                      const int* __restrict__ cu_seqlens) {
+    pdl_trigger();
+    pdl_wait();
+    parts = fresh(parts);
+    state = fresh(state);
+    const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int t0 = cu_seqlens[b], q = cu_seqlens[b + 1] - t0;
+    if (q <= 0) return;
+    float* rec = state + (int64_t)slots[b] * record;
+    float keep[SSM_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < SSM_MAX_TAPS; ++j) {
+        if (j >= taps - 1) break;
+        const int from = j + q;                                          // where the input of new place j lies now
+        keep[j] = from >= taps - 1 ? sum_parts(parts, splits, split_stride, (int64_t)(t0 + from - (taps - 1)) * cols + first_col + c)
+                                   : rec[(int64_t)from * channels + c];
+    }
+#pragma unroll
+    for (int j = 0; j < SSM_MAX_TAPS; ++j) {
+        if (j >= taps - 1) break;
+        rec[(int64_t)j * channels + c] = keep[j];
+    }
+}
+
+// grid (sequences * H, ceil(P / (threads / LN))).  A thread keeps `per` numbers of one column of S (the state rows
+// sub, sub + LN, ...); the LN threads of a column are neighbours in a warp.  Tokens pass in runs of `run` through shared
+// memory: x [run][cpb], B and C [run][N], dt and decay [run], y [run][cpb].
+template <int LN>
+__global__ void __launch_bounds__(128)
+ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __restrict__ parts, int splits, int64_t split_stride,
+                int cols, int dt_col, int H, int P, int N, int G, const float* __restrict__ dt_bias,
+                const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state, int64_t record,
+                int64_t state_off, const int* __restrict__ slots, const int* __restrict__ cu_seqlens, float* __restrict__ y,
+                int run) {
+    extern __shared__ float smem[];
+    pdl_trigger();
+    pdl_wait();
+    xbc = fresh(xbc);
+    parts = fresh(parts);
+    state = fresh(state);
+    constexpr int CPB = 128 / LN;                                        // columns a block takes
+    const int b = blockIdx.x / H, h = blockIdx.x - b * H, g = h / (H / G);
+    const int t0 = cu_seqlens[b], q = cu_seqlens[b + 1] - t0;
+    if (q <= 0) return;
+    const int tid = threadIdx.x, sub = tid % LN, lc = tid / LN, col = blockIdx.y * CPB + lc;
+    const int per = (N + LN - 1) / LN, inner = H * P;
+    float* xs = smem;                                                    // [run][CPB]
+    float* bs = xs + run * CPB;                                          // [run][N]
+    float* cs = bs + run * N;                                            // [run][N]
+    float* dts = cs + run * N;                                           // [run]
+    float* das = dts + run;                                              // [run]
+    float* ys = das + run;                                               // [run][CPB]
+    float* sp = state + (int64_t)slots[b] * record + state_off + ((int64_t)h * P + col) * N;
+    float S[SSM_ROWS];
+#pragma unroll
+    for (int r = 0; r < SSM_ROWS; ++r) {
+        const int n = sub + r * LN;
+        S[r] = (r < per && n < N && col < P) ? sp[n] : 0.f;
+    }
+    const float bias = dt_bias[h], rate = -expf(a_log[h]), skip = d_skip ? d_skip[h] : 0.f;
+    for (int i0 = 0; i0 < q; i0 += run) {
+        const int len = min(run, q - i0);
+        __syncthreads();
+        for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
+            const int i = idx / CPB, c = idx - i * CPB, pc = blockIdx.y * CPB + c;
+            xs[idx] = pc < P ? xbc[(int64_t)(t0 + i0 + i) * channels + h * P + pc] : 0.f;
+        }
+        for (int idx = tid; idx < len * N; idx += blockDim.x) {
+            const int i = idx / N, n = idx - i * N;
+            const float* rowp = xbc + (int64_t)(t0 + i0 + i) * channels + inner + g * N + n;
+            bs[idx] = rowp[0];
+            cs[idx] = rowp[G * N];
+        }
+        for (int i = tid; i < len; i += blockDim.x) {
+            const float dt = softplus_f(sum_parts(parts, splits, split_stride, (int64_t)(t0 + i0 + i) * cols + dt_col + h) + bias);
+            dts[i] = dt;
+            das[i] = expf(rate * dt);
+        }
+        __syncthreads();
+        for (int i = 0; i < len; ++i) {
+            const float xv = xs[i * CPB + lc], dt = dts[i], da = das[i];
+            const float* bi = bs + i * N;
+            const float* ci = cs + i * N;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < SSM_ROWS; ++r) {
+                const int n = sub + r * LN;
+                if (r < per && n < N) {
+                    S[r] = fmaf(da, S[r], (dt * bi[n]) * xv);
+                    acc = fmaf(S[r], ci[n], acc);
+                }
+            }
+#pragma unroll
+            for (int o = LN / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (sub == 0) ys[i * CPB + lc] = fmaf(skip, xv, acc);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
+            const int i = idx / CPB, c = idx - i * CPB, pc = blockIdx.y * CPB + c;
+            if (pc < P) y[(int64_t)(t0 + i0 + i) * inner + h * P + pc] = ys[idx];
+        }
+    }
+    if (col < P) {
+#pragma unroll
+        for (int r = 0; r < SSM_ROWS; ++r) {
+            const int n = sub + r * LN;
+            if (r < per && n < N) sp[n] = S[r];
+        }
+    }
+}
+
+// One block per token: g = y * silu(z) into shared memory; a warp takes whole runs (its lanes a run's elements in
+// steps of 32, the 32 sums by the butterfly); then out = g * factor of its run * w.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssm_gate_norm_kernel(const float* __restrict__ y, const float* __restrict__ parts, int splits, int64_t split_stride, int cols,
+                     int z_col, int inner, int n_runs, const float* __restrict__ w, float eps, T* __restrict__ out) {
+    extern __shared__ float smem[];
+    float* row = smem;                                                   // [inner]
+    float* factor = smem + ((inner + 3) & ~3);                           // [n_runs]
+    pdl_trigger();
+    pdl_wait();
+    y = fresh(y);
+    parts = fresh(parts);
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    for (int j = tid; j < inner; j += blockDim.x)
+        row[j] = y[(int64_t)t * inner + j] * silu_f(sum_parts(parts, splits, split_stride, (int64_t)t * cols + z_col + j));
+    __syncthreads();
+    const int len = inner / n_runs;
+    for (int r = warp; r < n_runs; r += n_warps) {
+        float ss = 0.f;
+        for (int j = lane; j < len; j += 32) ss = fmaf(row[r * len + j], row[r * len + j], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) factor[r] = 1.0f / sqrtf(ss / (float)len + eps);
+    }
+    __syncthreads();
+    for (int j = tid; j < inner; j += blockDim.x) st(out + (int64_t)t * inner + j, (row[j] * factor[j / len]) * w[j]);
+}
+
+template <int LN>
+int scan_launch(int n_seqs, int H, int P, int N, size_t smem, cudaStream_t s, const float* xbc, int channels, const float* parts,
+                int splits, int64_t split_stride, int cols, int dt_col, int G, const float* dt_bias, const float* a_log,
+                const float* d_skip, float* state, int64_t record, int64_t state_off, const int* slots, const int* cu_seqlens,
+                float* y, int run) {
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        WICK_CUDA(cudaFuncSetAttribute(ssm_scan_kernel<LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        raised = true;
+    }
+    WICK_CUDA(launch(ssm_scan_kernel<LN>, dim3(n_seqs * H, ceil_div(P, 128 / LN)), dim3(128), smem, s, xbc, channels, parts, splits,
+                     split_stride, cols, dt_col, H, P, N, G, dt_bias, a_log, d_skip, state, record, state_off, slots, cu_seqlens, y,
+                     run));
+    return check_launch("ssm_scan");
+}
+
+}  // namespace wick
+
+using namespace wick;
+typedef __nv_bfloat16 bf16;
+
+// parts: float32 [splits, n, cols] laid out [z | x | B | C | dt]; state: float32 [slots, record]; xbc: float32
+// [n, channels] and y: float32 [n, H P], both written here.  max_q: the most tokens a sequence can bring.
+WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H, int P, int N, int G, int taps, const float* conv_w,
+                          const float* conv_b, const float* dt_bias, const float* a_log, const float* d_skip, float* state,
+                          int64_t record, const int* slots, int n_seqs, const int* cu_seqlens, const int* start,
+                          const int* seq_of_token, const int* positions, float* xbc, float* y, int max_q, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    WICK_REQUIRE(H > 0 && P > 0 && N > 0 && G > 0 && H % G == 0, "ssm_mix: bad sizes");
+    WICK_REQUIRE(taps >= 1 && taps <= SSM_MAX_TAPS, "ssm_mix: %d taps (1 .. %d are built)", taps, SSM_MAX_TAPS);
+    WICK_REQUIRE(N <= 32 * SSM_ROWS, "ssm_mix: a state of %d numbers (up to %d are built)", N, 32 * SSM_ROWS);
+    const int inner = H * P, channels = inner + 2 * G * N;
+    WICK_REQUIRE(cols == 2 * inner + 2 * G * N + H, "ssm_mix: rows of %d numbers, %d expected", cols, 2 * inner + 2 * G * N + H);
+    WICK_REQUIRE(record == (int64_t)(taps - 1) * channels + (int64_t)H * P * N, "ssm_mix: records of another size");
+    WICK_REQUIRE(splits >= 1, "ssm_mix: partial sums are needed");
+    if (n == 0 || n_seqs == 0) return 0;
+    const int64_t stride = (int64_t)n * cols;
+    WICK_CUDA(launch(ssm_conv_kernel, dim3(n, ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride, cols, inner, channels,
+                     taps, conv_w, conv_b, (const float*)state, record, slots, seq_of_token, positions, start, xbc));
+    if (check_launch("ssm_conv")) return 1;
+    if (taps > 1) {
+        WICK_CUDA(launch(ssm_conv_state_kernel, dim3(n_seqs, ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride, cols,
+                         inner, channels, taps, state, record, slots, cu_seqlens));
+        if (check_launch("ssm_conv_state")) return 1;
+    }
+    int ln = 1;
+    while (ln < 32 && (N + ln - 1) / ln > SSM_ROWS) ln *= 2;
+    if (ln < 4 && N >= 16) ln = 4;                                       // (a thread keeps a few numbers, not a whole column)
+    const int cpb = 128 / ln;
+    int run = (40 * 1024 / 4) / (2 * cpb + 2 * N + 2);
+    run = run < 1 ? 1 : (run > 64 ? 64 : run);
+    if (run > max_q && max_q >= 1) run = max_q;
+    const size_t smem = (size_t)run * (2 * cpb + 2 * N + 2) * sizeof(float);
+    const int64_t state_off = (int64_t)(taps - 1) * channels;
+#define WICK_SCAN(LN)                                                                                                          \
+    return scan_launch<LN>(n_seqs, H, P, N, smem, s, xbc, channels, parts, splits, stride, cols, 2 * inner + 2 * G * N, G, dt_bias, \
+                           a_log, d_skip, state, record, state_off, slots, cu_seqlens, y, run)
+    switch (ln) {
+        case 1: WICK_SCAN(1);
+        case 2: WICK_SCAN(2);
+        case 4: WICK_SCAN(4);
+        case 8: WICK_SCAN(8);
+        case 16: WICK_SCAN(16);
+        default: WICK_SCAN(32);
+    }
+#undef WICK_SCAN
+    return 0;
+}
+
+// y: float32 [n, inner]; parts as above (z in its first columns); w: float32 [inner]; out: [n, inner].
+#define WICK_SSM_GATE_NORM(NAME, T)                                                                                            \
+    WICK_API int NAME(const float* y, const float* parts, int splits, int n, int cols, int inner, int n_runs, const float* w,    \
+                      float eps, void* out, void* s) {                                                                         \
+        WICK_REQUIRE(n_runs > 0 && inner % n_runs == 0 && inner <= cols, "ssm_gate_norm: bad sizes");                          \
+        if (n == 0) return 0;                                                                                                  \
+        const size_t smem = (size_t)(((inner + 3) & ~3) + n_runs) * sizeof(float);                                             \
+        WICK_REQUIRE(smem <= 48 * 1024, "ssm_gate_norm: a row of %d numbers is beyond one block's shared memory", inner);      \
+        WICK_CUDA(launch(ssm_gate_norm_kernel<T>, dim3(n), dim3(256), smem, (cudaStream_t)s, y, parts, splits,                 \
+                         (int64_t)n * cols, cols, 0, inner, n_runs, w, eps, (T*)out));                                          \
+        return check_launch("ssm_gate_norm");                                                                                  \
+    }
+WICK_SSM_GATE_NORM(wick_ssm_gate_norm_bf16, bf16)
+WICK_SSM_GATE_NORM(wick_ssm_gate_norm_f32, float)

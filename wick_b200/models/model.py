@@ -117,26 +117,36 @@ class Model:
             b = self.blocks[e.layer]
             n += b.mixer.weight_bytes() + b.ffn.weight_bytes() + b.mixer_norm.weight_bytes() + b.ffn_norm.weight_bytes()
             n += b.weight_bytes() + (b.side.weight_bytes() if b.side is not None else 0)
+            if e.before is not None:
+                n += self.shared[e.before].weight_bytes()
         return n
 
     def prompt_capturable(self) -> bool:
         """Whether every part reads a prompt step's shape from the device only, so that a
         captured prompt step can be replayed for other prompts of the same padded size."""
-        parts: List[Part] = [self.embedding, self.final_norm, self.head]
+        parts: List[Part] = [self.embedding, self.final_norm, self.head] + list(self.shared.values())
         for b in self.blocks:
             parts += [b, b.mixer, b.mixer_norm, b.ffn, b.ffn_norm] + ([b.side] if b.side is not None else [])
         return all(p.PROMPT_CAPTURABLE for p in parts)
 
     # ---- forward -------------------------------------------------------------
-    def forward(self, batch, cache) -> torch.Tensor:
+    def forward(self, batch, cache, tap: Optional[Callable[[int, torch.Tensor], None]] = None) -> torch.Tensor:
         """Run the batch's tokens through every scheduled layer, appending to the
-        cache, and return float32 logits [len(batch.want), vocab]."""
+        cache, and return float32 logits [len(batch.want), vocab].  ``tap(i, x)`` is called
+        after schedule entry ``i`` with the residual stream as that entry leaves it
+        (float32 [tokens, width], everything added)."""
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
         h = Hidden(self.embedding.forward(batch.tokens))
+        if any(getattr(p, "NEEDS_EMBEDDING_OUTPUT", False) for p in self.shared.values()):
+            batch.memo["embedding_output"] = h.x.clone()         # (the stream itself is changed in place by the layers)
         for i, e in enumerate(self.spec.schedule):
+            if e.before is not None:
+                self.shared[e.before].forward(h, batch)
             src = i if e.read_cache_of is None else e.read_cache_of
             h = self.blocks[e.layer].forward(h, batch, cache.view(src, batch), e.read_cache_of is None)
+            if tap is not None:
+                tap(i, h.resolved())
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.ctx.device)
         if h.pending is not None and (h.scale is not None or h.rms is not None):

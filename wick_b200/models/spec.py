@@ -62,10 +62,13 @@ class SharedPart:
 @dataclasses.dataclass(frozen=True)
 class ScheduleEntry:
     """Run ``layer``.  ``read_cache_of`` is the index (in the schedule) of an
-    earlier entry whose cache this entry's mixer reads without writing."""
+    earlier entry whose cache this entry's mixer reads without writing.  ``before`` names
+    the place of a shared part of the category ``side`` that changes the stream right before
+    the layer runs (what a pass over a range of layers begins with)."""
 
     layer: int
     read_cache_of: Optional[int] = None
+    before: Optional[str] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -88,7 +91,10 @@ class ModelSpec:
 
     def validate(self) -> None:
         n = len(self.layers)
+        sides = {sp.place for sp in self.shared if sp.category == "side"}
         for i, e in enumerate(self.schedule):
+            if e.before is not None and e.before not in sides:
+                raise ValueError(f"schedule[{i}] runs {e.before!r} first, which is no shared side part of the model")
             if not 0 <= e.layer < n:
                 raise ValueError(f"schedule[{i}] names layer {e.layer}, model has {n}")
             if e.read_cache_of is not None and not 0 <= e.read_cache_of < i:

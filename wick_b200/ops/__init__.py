@@ -522,7 +522,7 @@ def attention_decode_parts_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, hea
 # Mechanisms of layers beyond the plain pre-norm decoder: the norm after the residual sum, a
 # feed-forward's squared ReLU, the soft cap of logits, attention with options (csrc/attn_masked.cu)
 # and experts chosen by a table (csrc/moe.cu).
-LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "attn_multi.cu", "moe.cu"]
+LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "attn_multi.cu", "moe.cu", "ssm.cu"]
 
 MASKS = {"causal": 0, "block": 1, "window": 2}
 PAIRINGS = {"neighbours": 0, "halves": 1}
@@ -879,21 +879,26 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
                sin: Optional[torch.Tensor] = None, rot_dims: int = 0, pairing: str = "neighbours", maps: int = 1,
                v_keep: Optional[torch.Tensor] = None, v_mode: int = 0,
                blend: Optional[torch.Tensor] = None, kv: Optional[torch.Tensor], page_table: torch.Tensor,
-               seq_of_token: torch.Tensor, positions: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
-    """From the q/k/v projection's float32 partial sums ``parts`` [splits, n, H d + G d + G e]:
+               seq_of_token: torch.Tensor, positions: torch.Tensor, write_kv: bool = True,
+               q_span: Optional[int] = None, k_span: Optional[int] = None, norm_after_rotation: bool = False,
+               keys_are_values: bool = False) -> torch.Tensor:
+    """From the q/k/v projection's float32 partial sums ``parts`` [splits, n, H d + G d + G e (+ more)]:
     biases, RMS norms of q and k over spans the length of their weight vectors (a head, or the
-    whole projection), rotation of the first ``rot_dims`` elements of every q and k head by the
+    whole projection; ``q_span`` / ``k_span`` without a weight vector: the span is divided by its root
+    mean square and no more), rotation of the first ``rot_dims`` elements of every q and k head by the
     angles whose ``cos`` and ``sin`` [n, rot_dims / 2] are given (``pairing``: which two elements
-    turn together; ``maps``: a head is that many vectors side by side, each turned on its own), the value blend
+    turn together; ``maps``: a head is that many vectors side by side, each turned on its own;
+    ``norm_after_rotation``: the norm follows the rotation), the value blend
     (``v_mode`` 1: the values are also kept in ``v_keep`` [n, G e]; 2: v <- (1 - blend) v + blend
-    v_keep), then q -> the result [n, H, d] in ``dtype`` and k, v -> the token's place in ``kv``."""
+    v_keep), then q -> the result [n, H, d] in ``dtype`` and k, v -> the token's place in ``kv``.
+    ``keys_are_values``: the rows hold no values; a head's value is its key as projected, before norm
+    and rotation.  Columns behind q, k and v (an output gate's) are left alone."""
     _cuda("parts", parts, torch.float32)
-    W = (n_heads + n_kv) * d + n_kv * e
-    _need(parts.dim() == 3 and parts.shape[2] == W, f"parts must be [splits, n, {W}], is {tuple(parts.shape)}")
-    n = parts.shape[1]
+    W = (n_heads + n_kv) * d + (0 if keys_are_values else n_kv * e)
+    _need(parts.dim() == 3 and parts.shape[2] >= W, f"parts must be [splits, n, {W} or more], is {tuple(parts.shape)}")
+    n, cols = parts.shape[1], parts.shape[2]
     if bias is not None:
         _cuda("bias", bias, torch.float32, (W,))
-    q_span = k_span = 0
     if q_weight is not None:
         _cuda("q_weight", q_weight, torch.float32)
         q_span = q_weight.numel()
@@ -915,12 +920,58 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
     _cuda("positions", positions, torch.int32, (n,))
     q_out = torch.empty((n, n_heads, d), dtype=dtype, device=parts.device)
     _need(maps >= 1 and d % maps == 0, f"a head of {d} numbers is not {maps} vectors")
-    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifppiiipippppippip", _p(parts), parts.shape[0], n, _p(bias),
-                  n_heads, n_kv, d, e, _p(q_weight), q_span, _p(k_weight), k_span, float(eps), _p(cos), _p(sin),
+    flags = (1 if keys_are_values else 0) | (2 if norm_after_rotation else 0)
+    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifppiiipippppippiiip", _p(parts), parts.shape[0], n, _p(bias),
+                  n_heads, n_kv, d, e, _p(q_weight), int(q_span or 0), _p(k_weight), int(k_span or 0), float(eps), _p(cos), _p(sin),
                   rot_dims if cos is not None else 0, PAIRINGS[pairing], int(maps), _p(v_keep), v_mode, _p(blend), _p(q_out),
                   _p(kv) if write_kv else None, _p(page_table), page_table.shape[-1], _p(seq_of_token), _p(positions),
-                  1 if write_kv else 0, _stream())
+                  1 if write_kv else 0, int(cols), flags, _stream())
     return q_out
+
+
+def gate_rows_(y: torch.Tensor, parts: torch.Tensor, first_col: int) -> torch.Tensor:
+    """y[t, j] <- y[t, j] * sigmoid(g[t, j]) in place, g the sum (in index order) of the float32 partial sums
+    ``parts`` [splits, n, cols] at the columns from ``first_col`` on; the sigmoid is evaluated in float32."""
+    _cuda("y", y)
+    _cuda("parts", parts, torch.float32)
+    n, width = y.shape[0], y[0].numel()
+    _need(parts.dim() == 3 and parts.shape[1] == n and first_col + width <= parts.shape[2],
+          f"parts must be [splits, {n}, {first_col + width} or more], is {tuple(parts.shape)}")
+    _layer().call(f"wick_gate_rows_{_dt(y)}", "ppiiiiip", _p(y), _p(parts), parts.shape[0], n, width, parts.shape[2], int(first_col),
+                  _stream())
+    return y
+
+
+def weighted_sum(terms, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [1, n, width]: f_0 sum(a_0) + f_1 sum(a_1) + ... for ``terms`` = [(a_i float32 [splits_i, n, width], f_i)];
+    every a_i's partial sums are added in index order, the terms in the order given.  At most four terms."""
+    _need(1 <= len(terms) <= 4, "one to four terms")
+    a0 = terms[0][0]
+    _cuda("term", a0, torch.float32)
+    n, width = a0.shape[1], a0.shape[2]
+    ptrs, splits, factors = [], [], []
+    for a, f in terms:
+        _cuda("term", a, torch.float32)
+        _need(a.dim() == 3 and tuple(a.shape[1:]) == (n, width), f"every term must be [splits, {n}, {width}]")
+        ptrs.append(_p(a)); splits.append(a.shape[0]); factors.append(float(f))
+    while len(ptrs) < 4:
+        ptrs.append(None); splits.append(0); factors.append(0.0)
+    if out is None:
+        out = torch.empty((1, n, width), dtype=torch.float32, device=a0.device)
+    _layer().call("wick_weighted_sum", "pifpifpifpifplp", ptrs[0], splits[0], factors[0], ptrs[1], splits[1], factors[1],
+                  ptrs[2], splits[2], factors[2], ptrs[3], splits[3], factors[3], _p(out), n * width, _stream())
+    return out
+
+
+def concat_activation(a: torch.Tensor, b: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """[a | b] row by row in ``dtype``: a, b float32 [n, wa], [n, wb] -> [n, wa + wb]."""
+    _cuda("a", a, torch.float32)
+    _cuda("b", b, torch.float32)
+    _need(a.dim() == 2 and b.dim() == 2 and a.shape[0] == b.shape[0], "two matrices of as many rows")
+    n, wa, wb = a.shape[0], a.shape[1], b.shape[1]
+    out = torch.empty((n, wa + wb), dtype=dtype, device=a.device)
+    _layer().call(f"wick_concat_activation_{_dt(out)}", "pppiiip", _p(a), _p(b), _p(out), n, wa, wb, _stream())
+    return out
 
 
 def attention_masked_kind(d: int, v_dim: int, dtype: torch.dtype, is_decode: bool, plain: bool = False) -> str:
@@ -1071,6 +1122,120 @@ def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weight: float, base: Opti
     out = torch.empty((n, width), dtype=torch.float32, device=y.device)
     _layer().call("wick_moe_combine", "ppifpipiip", _p(y), _p(row_of), top, float(weight), _p(base), splits, _p(out), n, width,
                   _stream())
+    return out
+
+
+# ---- experts chosen by a router ---------------------------------------------------------------------------------------
+def moe_router(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, *, renormalize: bool = False
+               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """From the router's logits (float32 partial sums [splits, n, outputs]): scores = softmax over the outputs; the ``top``
+    outputs with the largest score + ``correction`` (float32 [outputs] or None) are chosen, the lowest index among equals.
+    Returns (choice int32 [n, top], weight float32 [n, top]: the chosen outputs' scores, divided by their sum if
+    ``renormalize``; ident int32 [n] = 0 .. n - 1: with it as token ids, ``choice`` is the table of the kernels that
+    read experts from a table)."""
+    _cuda("logits", logits, torch.float32)
+    _need(logits.dim() == 3, "the router's logits come as partial sums [splits, n, outputs]")
+    splits, n, n_out = logits.shape
+    if correction is not None:
+        _cuda("correction", correction, torch.float32, (n_out,))
+    choice = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    ident = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _layer().call("wick_moe_router", "piiipiipppp", _p(logits), splits, n, n_out, _p(correction), int(top), 1 if renormalize else 0,
+                  _p(choice), _p(weight), _p(ident), _stream())
+    return choice, weight, ident
+
+
+def moe_expert_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+    """float32 y [n * top, width]: y[t * top + c] = down[table[tokens[t], c]] hidden[t, c]; rows of pairs whose table entry
+    names no expert are zero.  down [experts, width, ff]."""
+    _cuda("hidden", hidden)
+    n, top, ff = hidden.shape
+    _cuda("tokens", tokens, torch.int32, (n,))
+    _cuda("table", table, torch.int32)
+    _need(table.shape[1] == top, "the table's width is the number of choices")
+    _cuda("down", down, hidden.dtype)
+    _need(down.dim() == 3 and down.shape[2] == ff, "down must be [experts, width, ff]")
+    width = down.shape[1]
+    y = torch.zeros((n * top, width), dtype=torch.float32, device=hidden.device)
+    _layer().call(f"wick_moe_expert_down_{_dt(hidden)}", "pppiippiiip", _p(hidden), _p(tokens), _p(table), top, down.shape[0], _p(down),
+                  _p(y), n, width, ff, _stream())
+    return y
+
+
+def moe_combine_weighted(y: torch.Tensor, row_of: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
+                         x: Optional[torch.Tensor], n_experts: int) -> torch.Tensor:
+    """float32 out[t] = sum over c of weight[t, c] * r(t, c): r is row ``row_of[t, c]`` of ``y`` (row t * top + c without
+    ``row_of``) where ``choice[t, c]`` < ``n_experts``, and ``x[t]`` itself where it is ``n_experts`` or more (an expert
+    that returns its input; nothing if ``x`` is None).  y float32 [rows, width]; x [n, width]."""
+    _cuda("y", y, torch.float32)
+    _cuda("choice", choice, torch.int32)
+    n, top = choice.shape
+    _cuda("weight", weight, torch.float32, (n, top))
+    width = y.shape[1]
+    if row_of is not None:
+        _cuda("row_of", row_of, torch.int32, (n, top))
+    dt = "f32"
+    if x is not None:
+        _cuda("x", x, None, (n, width))
+        dt = _dt(x)
+    out = torch.empty((n, width), dtype=torch.float32, device=y.device)
+    _layer().call(f"wick_moe_combine_weighted_{dt}", "pppppiipiip", _p(y), _p(row_of), _p(choice), _p(weight), _p(x), int(n_experts),
+                  top, _p(out), n, width, _stream())
+    return out
+
+
+# ---- a state-space recurrence with its short convolution ----------------------------------------------------------------
+def ssm_record_floats(heads: int, head_dim: int, state: int, groups: int, taps: int) -> int:
+    """float32 numbers of one sequence's record: the convolution's last ``taps`` - 1 inputs, then the state."""
+    return (taps - 1) * (heads * head_dim + 2 * groups * state) + heads * head_dim * state
+
+
+def ssm_mix(parts: torch.Tensor, *, heads: int, head_dim: int, state: int, groups: int, taps: int, conv_w: torch.Tensor,
+            conv_b: Optional[torch.Tensor], dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: Optional[torch.Tensor],
+            records: torch.Tensor, batch) -> torch.Tensor:
+    """The recurrence of a step's tokens.  ``parts``: the input projection's float32 partial sums [splits, n, cols], a row
+    laid out [z: H P | x: H P | B: G N | C: G N | dt: H].  x, B and C pass a causal convolution per channel (``conv_w``
+    [channels, taps], the last tap the token's own; zeros before position 0) and silu; dt <- softplus(dt + dt_bias);
+    per head S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x.  ``records``: float32 [slots, record], a
+    sequence's last inputs and state (see :func:`ssm_record_floats`), read and brought up to date for the slots of
+    ``batch``.  Returns y float32 [n, H P]."""
+    _cuda("parts", parts, torch.float32)
+    _need(parts.dim() == 3, "the projection comes as partial sums [splits, n, cols]")
+    splits, n, cols = parts.shape
+    inner, channels = heads * head_dim, heads * head_dim + 2 * groups * state
+    _cuda("conv_w", conv_w, torch.float32, (channels, taps))
+    if conv_b is not None:
+        _cuda("conv_b", conv_b, torch.float32, (channels,))
+    _cuda("dt_bias", dt_bias, torch.float32, (heads,))
+    _cuda("a_log", a_log, torch.float32, (heads,))
+    if d_skip is not None:
+        _cuda("d_skip", d_skip, torch.float32, (heads,))
+    _cuda("records", records, torch.float32)
+    record = ssm_record_floats(heads, head_dim, state, groups, taps)
+    _need(records.dim() == 2 and records.shape[1] == record, f"records must be [slots, {record}], are {tuple(records.shape)}")
+    _need(n == batch.n_tokens, f"{n} rows, the batch has {batch.n_tokens} tokens")
+    xbc = torch.empty((n, channels), dtype=torch.float32, device=parts.device)
+    y = torch.empty((n, inner), dtype=torch.float32, device=parts.device)
+    max_q = 1 if batch.is_decode else 0          # (0: unknown to the host, as in a captured prompt step)
+    _layer().call("wick_ssm_mix", "piiiiiiiipppppplpippppppip", _p(parts), splits, n, cols, heads, head_dim, state, groups, taps,
+                  _p(conv_w), _p(conv_b), _p(dt_bias), _p(a_log), _p(d_skip), _p(records), record, _p(batch.slots), batch.n_seqs,
+                  _p(batch.cu_seqlens), _p(batch.start), _p(batch.seq_of_token), _p(batch.positions), _p(xbc), _p(y), max_q,
+                  _stream(), kernels=3 if taps > 1 else 2)
+    return y
+
+
+def ssm_gate_norm(y: torch.Tensor, parts: torch.Tensor, weight: torch.Tensor, eps: float, runs: int, dtype: torch.dtype) -> torch.Tensor:
+    """g = y * silu(z), z the first columns of the float32 partial sums ``parts`` [splits, n, cols]; each of ``runs`` equal
+    parts of g is divided by its own root mean square and multiplied by ``weight``; [n, inner] in ``dtype``."""
+    _cuda("y", y, torch.float32)
+    _cuda("parts", parts, torch.float32)
+    n, inner = y.shape
+    _need(parts.dim() == 3 and parts.shape[1] == n and parts.shape[2] >= inner, "parts must be [splits, n, inner or more]")
+    _cuda("weight", weight, torch.float32, (inner,))
+    out = torch.empty((n, inner), dtype=dtype, device=y.device)
+    _layer().call(f"wick_ssm_gate_norm_{_dt(out)}", "ppiiiiipfpp", _p(y), _p(parts), parts.shape[0], n, parts.shape[2], inner, int(runs),
+                  _p(weight), float(eps), _p(out), _stream())
     return out
 
 

@@ -18,8 +18,12 @@ mixer          ``attention``           width, heads, kv_heads, head_dim, v_dim
                                        {"kind": "block" | "window", "size": n}),
                                        sink, value_blend (None or {"role":
                                        "source" | "blend", "group": key}),
+                                       qk_norm_weight (default True),
+                                       qk_norm_after_rotation (default False),
+                                       values (``own`` or ``keys``), gate,
                                        names (q, k, v, o, q_bias, k_bias, v_bias,
-                                       q_norm, k_norm, sink, blend -> local names)
+                                       q_norm, k_norm, sink, blend, gate -> local
+                                       names)
 =============  ======================  ==========================================
 
 The mixer, for a token at position p with input h (n tokens, H query heads of size d, G
@@ -28,8 +32,11 @@ key/value heads, values of size e):
 * q = Wq h (+ bq), k = Wk h (+ bk), v = Wv h (+ bv), one matrix product;
 * ``qk_norm``: RMS norm of q and of k with a weight vector, either per head (a weight of
   size d shared by the heads) or over the whole projection at once (weights of size H d and
-  G d), before the rotation;
+  G d), before the rotation; without ``qk_norm_weight`` the span is divided by its root mean
+  square and no more (no tensors); with ``qk_norm_after_rotation`` the norm follows the rotation;
 * the position encoding turns q and k;
+* ``values`` = ``keys``: there is no value matrix; a head's value is its key as projected,
+  before norm and rotation (so e = d);
 * ``value_blend``: the layer with the role ``source`` leaves its values (per token) in the
   step's memo under ``group``; a layer with the role ``blend`` replaces its own values by
   (1 - b) v + b v_source with its learned number b; what is cached is the blended value;
@@ -38,6 +45,8 @@ key/value heads, values of size e):
   sequence, wherever a prompt was cut), or the last ``size``;
 * weights exp(s_j) / (sum_j exp(s_j) + exp(sink_h)): the learned sink of a head adds to the
   denominator only;
+* ``gate``: the heads' results, side by side, are multiplied element by element by
+  sigmoid(Wg h), a matrix of H e rows that reads the mixer's own input (float32 sigmoid);
 * the heads' results, side by side, go through Wo.
 
 Everything after the projection up to the product with Wo is float32 except the stored q, k
@@ -164,6 +173,15 @@ class Attention(Mixer):
         self.qk_norm = p.get("qk_norm")
         if self.qk_norm not in (None, "head", "projection"):
             raise ValueError(f"qk_norm is None, 'head' or 'projection', not {self.qk_norm!r}")
+        self.qk_norm_weight = bool(p.get("qk_norm_weight", True))
+        self.norm_after_rotation = bool(p.get("qk_norm_after_rotation", False))
+        self.values = str(p.get("values", "own"))
+        if self.values not in ("own", "keys"):
+            raise ValueError(f"values are 'own' or 'keys', not {self.values!r}")
+        self.keys_are_values = self.values == "keys"
+        if self.keys_are_values and self.v_dim != self.head_dim:
+            raise ValueError("keys that are the values have the values' size")
+        self.has_gate = bool(p.get("gate", False))
         self.eps = float(p.get("eps", 0.0))
         mask = p.get("mask")
         self.mask, self.mask_size = "causal", 0
@@ -175,15 +193,20 @@ class Attention(Mixer):
         self.blend = p.get("value_blend")
         if self.blend is not None and self.blend.get("role") not in ("source", "blend"):
             raise ValueError(f"value_blend's role is 'source' or 'blend', not {self.blend}")
+        if self.keys_are_values:
+            if self.blend is not None or self.bias:
+                raise ValueError("keys that are the values are neither blended nor biased")
+            self.v_all = 0                       # (no rows of the projection)
+        self.gate_dim = self.heads * self.v_dim if self.has_gate else 0
         self.position = build_part("position", p.get("position") or PartSpec("none"), ctx)
         if not isinstance(self.position, (RotaryPairs, NoPosition)):
             raise ValueError("this mixer's kernel turns pairs (rotary_pairs) or nothing")
         names = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_bias="q_proj.bias",
                      k_bias="k_proj.bias", v_bias="v_proj.bias", q_norm="q_norm.weight", k_norm="k_norm.weight",
-                     sink="sinks", blend="value_blend")
+                     sink="sinks", blend="value_blend", gate="gate_proj.weight")
         names.update(p.get("names") or {})
         self.names = names
-        self.qkv = Linear(self.q_dim + self.k_dim + self.v_all, self.width, ctx)
+        self.qkv = Linear(self.q_dim + self.k_dim + self.v_all + self.gate_dim, self.width, ctx)   # rows: q, k, v, gate
         self.o = Linear(self.width, self.heads * self.v_dim, ctx)
         self.qkv_bias = self.q_weight = self.k_weight = self.sink = self.blend_factor = None
 
@@ -193,13 +216,17 @@ class Attention(Mixer):
 
     def tensor_specs(self):
         nm = self.names
-        specs = [TensorSpec(nm["q"], (self.q_dim, self.width)), TensorSpec(nm["k"], (self.k_dim, self.width)),
-                 TensorSpec(nm["v"], (self.v_all, self.width)), TensorSpec(nm["o"], (self.width, self.heads * self.v_dim))]
+        specs = [TensorSpec(nm["q"], (self.q_dim, self.width)), TensorSpec(nm["k"], (self.k_dim, self.width))]
+        if not self.keys_are_values:
+            specs.append(TensorSpec(nm["v"], (self.v_all, self.width)))
+        if self.has_gate:
+            specs.append(TensorSpec(nm["gate"], (self.gate_dim, self.width)))
+        specs.append(TensorSpec(nm["o"], (self.width, self.heads * self.v_dim)))
         if self.bias:
             specs += [TensorSpec(nm["q_bias"], (self.q_dim,), "vector", init="around_zero"),
                       TensorSpec(nm["k_bias"], (self.k_dim,), "vector", init="around_zero"),
                       TensorSpec(nm["v_bias"], (self.v_all,), "vector", init="around_zero")]
-        if self.qk_norm is not None:
+        if self.qk_norm is not None and self.qk_norm_weight:
             qn, kn = self._norm_sizes()
             specs += [TensorSpec(nm["q_norm"], (qn,), "vector"), TensorSpec(nm["k_norm"], (kn,), "vector")]
         if self.has_sink:
@@ -211,11 +238,12 @@ class Attention(Mixer):
 
     def load(self, fetch):
         nm, hold = self.names, self.ctx.hold
-        self.qkv.load_rows([fetch(nm["q"]), fetch(nm["k"]), fetch(nm["v"])])
+        self.qkv.load_rows([fetch(nm["q"]), fetch(nm["k"])] + ([] if self.keys_are_values else [fetch(nm["v"])])
+                           + ([fetch(nm["gate"])] if self.has_gate else []))
         self.o.load_rows([fetch(nm["o"])])
         if self.bias:
             self.qkv_bias = torch.cat([hold(fetch(nm[k]), "vector") for k in ("q_bias", "k_bias", "v_bias")])
-        if self.qk_norm is not None:
+        if self.qk_norm is not None and self.qk_norm_weight:
             self.q_weight, self.k_weight = hold(fetch(nm["q_norm"]), "vector"), hold(fetch(nm["k_norm"]), "vector")
         if self.has_sink:
             self.sink = hold(fetch(nm["sink"]), "vector")
@@ -228,16 +256,18 @@ class Attention(Mixer):
             return self.qkv.rows(0, q)
         if name == nm["k"]:
             return self.qkv.rows(q, q + k)
-        if name == nm["v"]:
+        if name == nm["v"] and not self.keys_are_values:
             return self.qkv.rows(q + k, q + k + self.v_all)
+        if self.has_gate and name == nm["gate"]:
+            return self.qkv.rows(q + k + self.v_all, q + k + self.v_all + self.gate_dim)
         if name == nm["o"]:
             return self.o.rows(0, self.width)
         if self.bias and name in (nm["q_bias"], nm["k_bias"], nm["v_bias"]):
             lo, hi = {nm["q_bias"]: (0, q), nm["k_bias"]: (q, q + k), nm["v_bias"]: (q + k, q + k + self.v_all)}[name]
             return self.qkv_bias[lo:hi].contiguous()
-        if self.qk_norm is not None and name == nm["q_norm"]:
+        if self.q_weight is not None and name == nm["q_norm"]:
             return self.q_weight
-        if self.qk_norm is not None and name == nm["k_norm"]:
+        if self.k_weight is not None and name == nm["k_norm"]:
             return self.k_weight
         if self.has_sink and name == nm["sink"]:
             return self.sink
@@ -255,7 +285,8 @@ class Attention(Mixer):
     # ---- forward ----
     def forward(self, x, batch, cache, write_cache):
         n = x.shape[0]
-        parts = self.qkv.forward_delta(x)                 # float32 [splits, n, H d + G d + G e]
+        parts = self.qkv.forward_delta(x)                 # float32 [splits, n, H d + G d + G e + gate's H e]
+        q_span, k_span = self._norm_sizes() if self.qk_norm is not None else (0, 0)
         v_keep, v_mode = None, 0
         if self.blend is not None:
             key = ("value_blend", self.blend.get("group"))
@@ -275,10 +306,14 @@ class Attention(Mixer):
             cos=cos, sin=sin, rot_dims=rot.dims if rot else 0,
             pairing=rot.pairing if rot else "neighbours", v_keep=v_keep, v_mode=v_mode, blend=self.blend_factor,
             kv=cache.kv, page_table=batch.page_table, seq_of_token=batch.seq_of_token, positions=batch.positions,
-            write_kv=write_cache)
+            write_kv=write_cache, q_span=q_span, k_span=k_span, norm_after_rotation=self.norm_after_rotation,
+            keys_are_values=self.keys_are_values)
         att = ops.attention_masked(q, cache.kv, batch, self.scale, n_kv=self.kv_heads, v_dim=self.v_dim, mask=self.mask,
                                    mask_size=self.mask_size, sink=self.sink)
-        return self.o.forward_delta(att.view(n, self.heads * self.v_dim))
+        att = att.view(n, self.heads * self.v_dim)
+        if self.has_gate:
+            ops.gate_rows_(att, parts, self.q_dim + self.k_dim + self.v_all)
+        return self.o.forward_delta(att)
 
 
 register_part("position", "rotary_pairs", RotaryPairs)

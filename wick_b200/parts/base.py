@@ -43,7 +43,9 @@ class TensorSpec:
     role's default (matrices N(0, std), vectors 1 + N(0, vector_std)) is none:
     ``around_zero`` (a vector that is added, or a norm weight stored as its distance from
     one), ``unit_interval`` (a blend factor), ``distinct_below`` (integer rows of different
-    values below ``init_arg``), ``absent`` (an optional tensor that random models leave out)."""
+    values below ``init_arg``), ``absent`` (an optional tensor that random models leave out),
+    ``conv_taps`` (a short filter's taps, N(0, 1 / taps)), ``router`` (rows whose scores differ
+    from token to token), ``mix_pair`` (a matrix [w, 2 w] near the sum of its two halves' inputs)."""
 
     name: str
     shape: Tuple[int, ...]
@@ -84,7 +86,9 @@ class CacheNeed:
     ``head_dim`` each, in pages (values ``v_head_dim`` each, if that is given and
     differs); ``window`` (tokens) if only the last ones are ever read.  kind ``paged_rows``:
     one row of ``shape`` per position, in the same pages.  kind ``state``: one record of fixed
-    ``shape`` and ``dtype`` per sequence, zeroed when the sequence starts."""
+    ``shape`` and ``dtype`` per sequence, zeroed when the sequence starts.  kind ``several``:
+    a mixer made of several keeps what each of ``parts`` asks for; its cache view's ``parts``
+    are the views of those, in order."""
 
     kind: str
     kv_heads: int = 0
@@ -93,6 +97,7 @@ class CacheNeed:
     shape: Tuple[int, ...] = ()
     dtype: Optional[torch.dtype] = None   # None: the compute dtype
     v_head_dim: Optional[int] = None      # None: as head_dim
+    parts: Tuple["CacheNeed", ...] = ()
 
 
 class Part:

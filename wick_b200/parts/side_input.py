@@ -1,4 +1,4 @@
-"""What a layer adds to the stream from the token ids.
+"""What changes the stream from something else than the stream alone.
 
 =============  ======================  ==========================================
 category       kind                    params
@@ -6,7 +6,12 @@ category       kind                    params
 side           ``gated_token_rows``    width, dim, offset, eps, table (the place
                                        of the model's shared table part), names
                                        (gate, proj, norm -> local names)
+side           ``mix_with_embedding``  width, tensor (local name of the matrix)
 =============  ======================  ==========================================
+
+``mix_with_embedding`` (a shared part that a schedule entry names in ``before``): with x the stream
+and x0 the embedding's output for the same token, x <- W [x; x0], W of shape [width, 2 width] with the
+stream's columns first.  The stream is replaced, not added to.
 
 With x the stream after the layer's feed-forward and e the ``dim`` numbers from ``offset``
 on of the token's row in the shared table:  g = gelu(Wgate x) * e  (gelu in its tanh
@@ -76,4 +81,38 @@ class GatedTokenRows(SideInput):
         h.defer(self.proj.forward_delta(g), rms=(self.norm_weight, self.eps))
 
 
+class MixWithEmbedding(SideInput):
+    PROMPT_CAPTURABLE = True
+    NEEDS_EMBEDDING_OUTPUT = True          # the model leaves the embedding's output in the step's memo
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width = int(params["width"])
+        self.name = str(params.get("tensor", "weight"))
+        self.mix = Linear(self.width, 2 * self.width, ctx)
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.width, 2 * self.width), init="mix_pair")]
+
+    def load(self, fetch):
+        self.mix.load_rows([fetch(self.name)])
+
+    def tensor(self, name):
+        return self.mix.rows(0, self.width) if name == self.name else None
+
+    def weight_bytes(self):
+        return self.mix.weight_bytes()
+
+    def forward(self, h, batch):
+        x0 = batch.memo.get("embedding_output")
+        if x0 is None:
+            raise RuntimeError("the step's memo holds no embedding output")
+        x = h.resolved()
+        both = ops.concat_activation(x, x0, self.ctx.dtype)           # [n, 2 width]: the stream, then the embedding's output
+        h.x = self.mix.forward(both, torch.float32)
+        h.act = None
+        h.defer(None)
+
+
 register_part("side", "gated_token_rows", GatedTokenRows)
+register_part("side", "mix_with_embedding", MixWithEmbedding)

@@ -19,7 +19,9 @@ ffn            ``gated_mlp``           width, intermediate, activation ("silu"),
                                        names (gate, up, down -> local names)
 block          ``prenorm_residual``    width and layer_scale (mixer, ffn -> local
                                        names of the two factors) where the
-                                       sublayers' results are scaled
+                                       sublayers' results are scaled; post_norm
+                                       (mixer, ffn -> local names, eps) where
+                                       they are normed before the sum
 block          ``postnorm_residual``   alpha
 embedding      ``table``               vocab, width, tensor
 head           ``linear``              vocab, width, tied, tensor, soft_cap
@@ -386,7 +388,10 @@ class PreNormResidual(Block):
     ``layer_scale`` (the local names of two float32 vectors of ``width`` numbers): the
     mixer's and the feed-forward's results are multiplied by them, element by element,
     before the sum; the factor travels with the pending sum, and the parts never add to
-    the stream themselves.  A layer whose feed-forward is of kind ``none`` ends after its
+    the stream themselves.  ``post_norm`` (the local names of two float32 vectors under ``mixer``
+    and ``ffn``, and ``eps``): a sublayer's result is divided by its root mean square and multiplied
+    by the vector before the sum, x <- x + rms(sublayer(norm(x))) * w; it travels with the pending
+    sum in the same way.  A layer whose feed-forward is of kind ``none`` ends after its
     mixer.  A ``side`` part, if the layer has one, runs last."""
 
     PROMPT_CAPTURABLE = True
@@ -394,32 +399,44 @@ class PreNormResidual(Block):
     def __init__(self, params, ctx, mixer, mixer_norm, ffn, ffn_norm):
         super().__init__(params, ctx, mixer, mixer_norm, ffn, ffn_norm)
         self.scale_names = dict(params.get("layer_scale") or {})
-        self.width = int(params["width"]) if self.scale_names else 0
+        post = dict(params.get("post_norm") or {})
+        self.post_eps = float(post.pop("eps", 0.0))
+        self.post_names = post
+        self.width = int(params["width"]) if self.scale_names or self.post_names else 0
         self.scales = {}
+        self.posts = {}
 
     def tensor_specs(self):
         no_ffn = getattr(self.ffn, "IS_NONE", False)
-        return [TensorSpec(nm, (self.width,), "vector", optional=(k == "ffn" and no_ffn), init="absent" if k == "ffn" and no_ffn else "")
-                for k, nm in self.scale_names.items()]
+        specs = [TensorSpec(nm, (self.width,), "vector", optional=(k == "ffn" and no_ffn), init="absent" if k == "ffn" and no_ffn else "")
+                 for k, nm in self.scale_names.items()]
+        return specs + [TensorSpec(nm, (self.width,), "vector", optional=(k == "ffn" and no_ffn),
+                                   init="absent" if k == "ffn" and no_ffn else "") for k, nm in self.post_names.items()]
 
     def load(self, fetch):
-        for k, nm in self.scale_names.items():
-            t = fetch(nm)
-            self.scales[k] = None if t is None else self.ctx.hold(t, "vector")
+        for names, held in ((self.scale_names, self.scales), (self.post_names, self.posts)):
+            for k, nm in names.items():
+                t = fetch(nm)
+                held[k] = None if t is None else self.ctx.hold(t, "vector")
 
     def tensor(self, name):
-        for k, nm in self.scale_names.items():
-            if nm == name:
-                return self.scales.get(k)
+        for names, held in ((self.scale_names, self.scales), (self.post_names, self.posts)):
+            for k, nm in names.items():
+                if nm == name:
+                    return held.get(k)
         return None
 
     def weight_bytes(self):
-        return sum(4 * self.width for v in self.scales.values() if v is not None)
+        return sum(4 * self.width for held in (self.scales, self.posts) for v in held.values() if v is not None)
+
+    def _post(self, which):
+        w = self.posts.get(which)
+        return None if w is None else (w, self.post_eps)
 
     def forward(self, h, batch, cache, write_cache):
         dt = self.ctx.dtype
         h.act = None                     # (this block changes the stream without keeping a copy)
-        scaled = bool(self.scale_names)
+        scaled = bool(self.scale_names) or bool(self.post_names)
         if h.pending is not None and (h.scale is not None or h.rms is not None):
             xn = self.mixer_norm.add_forward(h.x, h.pending, dt, scale=h.scale, rms=h.rms)
         elif h.pending is not None:
@@ -432,19 +449,19 @@ class PreNormResidual(Block):
         else:
             d = self.mixer.forward(xn, batch, cache, write_cache)
         if getattr(self.ffn, "IS_NONE", False):
-            h.defer(None if d is None else as_splits(d), self.scales.get("mixer"))
+            h.defer(None if d is None else as_splits(d), self.scales.get("mixer"), self._post("mixer"))
         else:
             if d is None:
                 xn = self.ffn_norm.forward(h.x, dt)
             elif scaled:
-                xn = self.ffn_norm.add_forward(h.x, as_splits(d), dt, scale=self.scales.get("mixer"))
+                xn = self.ffn_norm.add_forward(h.x, as_splits(d), dt, scale=self.scales.get("mixer"), rms=self._post("mixer"))
             else:
                 xn = self.ffn_norm.add_forward(h.x, as_splits(d), dt)
             if getattr(self.ffn, "ADDS_TO_RESIDUAL", False) and not scaled:
                 d = self.ffn.forward(xn, batch, residual=h.x)
             else:
                 d = self.ffn.forward(xn, batch)
-            h.defer(None if d is None else as_splits(d), self.scales.get("ffn"))
+            h.defer(None if d is None else as_splits(d), self.scales.get("ffn"), self._post("ffn"))
         if self.side is not None:
             self.side.forward(h, batch)
         return h

@@ -41,7 +41,17 @@ def _make(name: str, ts, seed: int, device, dtype: torch.dtype, std: float, vect
     if ts.init == "unit_interval":
         return (0.2 + 0.6 * torch.rand(ts.shape, generator=g, device=device, dtype=torch.float32)).to(dtype)
     t = torch.randn(ts.shape, generator=g, device=device, dtype=torch.float32)
-    if ts.init == "around_zero":
+    if ts.init == "conv_taps":                         # a short filter: taps that add up to something of the input's size
+        t = t / float(ts.shape[-1]) ** 0.5
+    elif ts.init == "router":                          # scores that differ from token to token
+        t = t / float(ts.shape[-1]) ** 0.5 * 4.0
+    elif ts.init == "mix_pair":                        # [x; x0] -> x: near the sum of the two halves' identities
+        half = ts.shape[1] // 2
+        t = std * t
+        eye = torch.eye(ts.shape[0], half, device=device, dtype=torch.float32)
+        t[:, :half] += 0.7 * eye
+        t[:, half:2 * half] += 0.7 * eye
+    elif ts.init == "around_zero":
         t = vector_std * t
     elif ts.role == "vector":
         t = 1.0 + vector_std * t
