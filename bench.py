@@ -2,7 +2,7 @@
 """Decode and prefill throughput of wick_b200 on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--model 8b|14b|32b]
-    python bench.py --design nibotar|tuguvik [--design-size 2k|4k]      (a line of its own, see below)
+    python bench.py --design nibotar|tuguvik|fasunex [--design-size 2k|4k]      (a line of its own, see below)
 
 The default run has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32
 heads over 8 kv heads of 128, intermediate 12288, vocabulary 151936) with random
@@ -35,6 +35,9 @@ launched one by one without programmatic dependent launch, so that they do not o
 and of attention through a cached latent, every layer with a gated feed-forward of Qwen3's
 intermediate size and a token input); its ``parts`` count each kernel's own arithmetic and
 bytes, so that every kind can be held against the measured peaks.
+``--design fasunex`` prints the line of the Fasunex design (layers that alternate between a chunked attention beside a
+state-space recurrence and an attention whose keys are its values, routed experts with identity outputs) beside Nibotar,
+the closest design here, at equal size, with the same kind of ``parts``.
 """
 import argparse
 import json
@@ -263,6 +266,8 @@ def design_step_bytes(eng, z, name, batch, kv_tokens):
         kv_tokens = min(kv_tokens, batch * z["mask"])
     if name == "tuguvik":
         kv_tokens = min(kv_tokens, batch * (z["window"] + z["keep_first"]))
+    if name == "fasunex":
+        return fasunex_step_bytes(eng, z, batch, kv_tokens)
     return n + eng.cache.read_bytes(int(kv_tokens), batch)
 
 
@@ -603,6 +608,188 @@ def tuguvik_compare(args) -> int:
     return 0 if all(m["finite"] for m in models.values()) else 1
 
 
+# ---- --design fasunex ----------------------------------------------------------
+# Fasunex beside Nibotar, the closest design here (attention over blocks of positions with a sink, experts): the same width,
+# heads, layers, vocabulary, block size and experts.  Layers alternate between the parallel mixer (chunked attention beside
+# a state-space recurrence of `ssm_heads` x `ssm_dim` numbers with a state of `ssm_state`) and the attention whose keys are
+# its values; every layer has routed experts with two identity outputs.
+def fasunex_configs(z):
+    d = z["dim"]
+    left = dict(heads=z["heads"], kv_heads=z["kv"], dim=d, vdim=d, scale=d ** -0.5, mask={"size": z["mask"]},
+                rot={"dims": d // 2, "base": 10000.0})
+    right = dict(heads=z["width"] // 64, vdim=64, state=128, groups=2, conv=4, norm_groups=2)
+    att = dict(heads=z["heads"], kv_heads=z["kv"], dim=d, vdim=d, scale=d ** -0.5)
+    mlp = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "identity": 2, "top": z["top"]}}
+    layers = [dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=mlp) if i % 2 == 0
+              else dict(type="attention", mixer=att, mlp=mlp) for i in range(z["layers"])]
+    fas = dict(architecture="Fasunex", vocab=z["vocab"], width=z["width"], norm={"eps": 1e-5}, layers=layers)
+    return {"fasunex": fas, "nibotar": design_configs(z)["nibotar"]}
+
+
+def fasunex_step_bytes(eng, z, batch, kv_tokens):
+    """Bytes a decode step of Fasunex has to read: the weights (of a layer's experts a batch uses E (1 - (1 - top / (E + I))^batch)
+    on average), the keys and values (a chunked layer reads at most one chunk a sequence) and the recurrences' records."""
+    n = eng.model.weight_bytes_per_step()
+    e, top, outs = z["experts"], z["top"], z["experts"] + 2
+    one = 3 * z["expert_ff"] * z["width"] * 2
+    n += z["layers"] * (e * (1.0 - (1.0 - top / outs) ** batch) - min(top, e)) * one
+    row = 2 * z["kv"] * z["dim"] * 2
+    half = z["layers"] // 2
+    n += (z["layers"] - half) * min(kv_tokens, batch * z["mask"]) * row + half * kv_tokens * row
+    for g in eng.cache.groups:
+        if g.need.kind == "state":
+            n += 2 * g.store.read_bytes(0, batch)                  # (read and written back)
+    return n
+
+
+def fasunex_parts(torch, wick, pk, z, name, cfg_json):
+    """What a 2,048-token prompt step and a decode step of 8 sequences (1,500 cached positions each) spend in each kind of
+    kernel: microseconds a step (all layers), and the kernels' own arithmetic and bytes over that time against the measured
+    peaks (tensor-core peak for the matrix products and the attention, copy bandwidth for the rest)."""
+    from wick_b200 import ops
+    from wick_b200.parts.linear import Linear
+    cfg = wick.config_from_json(cfg_json)
+    eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 1600 + PREFILL + 64, max_seqs=16, use_graphs=False)
+    acc = {}
+    ctx = {"pairs": 0, "kv_rows": 0, "blocked": True}
+
+    def timed(kind, fn, work):
+        def run(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(torch.cuda.current_stream())
+            r = fn(*a, **kw)
+            e1.record(torch.cuda.current_stream())
+            acc.setdefault(kind, []).append((e0, e1) + tuple(work(r, *a, **kw)))
+            return r
+        return run
+
+    def nbytes(*ts):
+        return sum(t.numel() * t.element_size() for t in ts if torch.is_tensor(t))
+
+    def product(kind, lin):
+        w = lin.out_features * lin.in_features
+        for fname in ("forward", "forward_delta"):
+            setattr(lin, fname, timed(kind, getattr(lin, fname),
+                                      lambda r, x, *a, **k: (2.0 * x.shape[0] * w, 2 * w + nbytes(x) + (nbytes(r) if r is not None else 4 * x.shape[0] * lin.out_features))))
+
+    def attn_work(r, q, kv, batch, scale, **kw):
+        n, H, d = q.shape
+        blocked = kw.get("mask", "causal") == "block"
+        pairs, rows = (ctx["pairs_block"], ctx["rows_block"]) if blocked else (ctx["pairs"], ctx["kv_rows"])
+        return 4.0 * pairs * H * d, nbytes(q, r) + rows * kv[0].numel() // 64 * kv.element_size()
+
+    def rows_work(r, *a, **k):
+        ts = [t for t in a if torch.is_tensor(t)] + [t for t in k.values() if torch.is_tensor(t) and t.dim() >= 2]
+        out = [t for t in (r if isinstance(r, tuple) else (r,)) if torch.is_tensor(t)]
+        return 0.0, nbytes(*[t for t in ts if t.numel() < (1 << 27)], *[t for t in out if not any(t is x for x in ts)])
+
+    def ssm_work(r, parts, **k):
+        n = parts.shape[1]
+        H, Pn, N = k["heads"], k["head_dim"], k["state"]
+        ch = H * Pn + 2 * k["groups"] * N
+        rec = 2 * 4 * k["batch"].n_seqs * (H * Pn * N + (k["taps"] - 1) * ch)
+        return 0.0, nbytes(parts) + 4 * n * (2 * ch + H * Pn) + rec
+
+    def norm_work(r, x, delta=None, *a, **k):
+        return 0.0, nbytes(x, delta) + (nbytes(x) if delta is not None and k.get("rows") is None else 0) + (nbytes(r) if r is not None and r is not x else 0)
+
+    def ffn_work(width, ff, top, share, shared_ff):
+        def work(r, x, *a, **k):
+            n = x.shape[0]
+            act = top * share * ff + shared_ff
+            return 2.0 * n * 3 * width * act, nbytes(x, r) + min(n * top, z["experts"]) * 3 * width * ff * 2 + 3 * width * shared_ff * 2
+        return work
+
+    for fname, kind, work in (("attention_masked", "attention", attn_work), ("qkv_finish", "finish", rows_work),
+                              ("gate_rows_", "output gate", rows_work), ("ssm_mix", "recurrence (convolution, scan)", ssm_work),
+                              ("ssm_gate_norm", "recurrence's gate and norm", rows_work), ("weighted_sum", "sum of the branches", rows_work),
+                              ("concat_activation", "pass input", rows_work), ("stream_update", "norm", norm_work),
+                              ("scaled_add_rmsnorm", "norm", lambda r, x, delta, *a, **k: norm_work(r, x, delta)),
+                              ("rmsnorm", "norm", lambda r, x, *a, **k: norm_work(r, x, k.get("delta"), rows=k.get("rows")))):
+        setattr(ops, fname, timed(kind, getattr(ops, fname), work))       # (the parts call these through the module)
+    W = z["width"]
+    for blk in eng.model.blocks:
+        mixers = getattr(blk.mixer, "branches", [blk.mixer])
+        for m in mixers:
+            for attr, kind in (("qkv", "projections into the mixer"), ("input", "projections into the mixer"), ("o", "o product")):
+                if isinstance(getattr(m, attr, None), Linear):
+                    product(kind, getattr(m, attr))
+        f = blk.ffn
+        if type(f).__name__ == "RoutedMoE":
+            work = ffn_work(W, f.intermediate, f.top, f.experts / float(f.outputs), 0)
+        elif type(f).__name__ == "TableMoE":
+            work = ffn_work(W, f.intermediate, f.top, 1.0, z["shared_ff"])
+        else:
+            work = ffn_work(W, z["dense_ff"], 1, 1.0, 0)
+        f.forward = timed("feed-forward " + type(f).__name__, f.forward, work)
+
+    def collect():
+        torch.cuda.synchronize()
+        res = {}
+        for kind, evs in acc.items():
+            us = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e3
+            fl, by = sum(e[2] for e in evs), sum(e[3] for e in evs)
+            r = res[kind] = {"us_per_step": us, "calls": len(evs)}
+            if fl:
+                r["tflops"] = fl / (us * 1e-6) / 1e12
+                r["tflops_frac"] = r["tflops"] / pk["bf16_tflops"]
+            r["gbs"] = by / (us * 1e-6) / 1e9
+            r["gbs_frac"] = r["gbs"] / pk["hbm_gbs"]
+        acc.clear()
+        return res
+
+    out = {}
+    blk = z["mask"]
+    ptoks = random_prompts(torch, z["vocab"], [PREFILL], 3)[0]
+    ctx["pairs"], ctx["kv_rows"] = sum(p + 1 for p in range(PREFILL)), PREFILL
+    ctx["pairs_block"], ctx["rows_block"] = sum(p % blk + 1 for p in range(PREFILL)), PREFILL
+    for i in range(3):
+        s = eng.open_seq()
+        acc.clear()
+        eng.step([s], [ptoks])
+        eng.close_seq(s)
+    out["prompt_2048"] = collect()
+    slots = [eng.open_seq() for _ in range(8)]
+    eng.step(slots, random_prompts(torch, z["vocab"], [1500] * 8, 4))
+    ctx["pairs"] = ctx["kv_rows"] = 8 * 1504
+    ctx["pairs_block"] = ctx["rows_block"] = 8 * (1503 % blk + 1)
+    for i in range(4):
+        acc.clear()
+        eng.step(slots, [[1 + i]] * 8)
+    out["decode_b8_ctx1500"] = collect()
+    return out
+
+
+def fasunex_compare(args) -> int:
+    import torch
+    import wick_b200 as wick
+    pk = peaks()
+    z = DESIGN_SIZES[args.design_size]
+    cfgs = fasunex_configs(z)
+    if args.design_parts:
+        print(json.dumps({args.design_parts: fasunex_parts(torch, wick, pk, z, args.design_parts, cfgs[args.design_parts])}))
+        return 0
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+    with Clocks() as clk:
+        models = {name: design_model(torch, wick, pk, z, name, cfgs[name], steps, warmup) for name in ("fasunex", "nibotar")}
+    env = dict(os.environ, WICK_B200_NO_PDL="1")
+    parts, errors = {}, {}
+    for name in ("fasunex", "nibotar"):                # (a process each: the timing wrappers replace the module's functions)
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", "fasunex", "--design-size", args.design_size,
+                            "--design-parts", name], env=env, capture_output=True, text=True)
+        for ln in r.stdout.splitlines():
+            if ln.startswith("{"):
+                parts.update(json.loads(ln))
+        if name not in parts:
+            errors[name] = r.stderr[-600:]
+    line = {"metric": f"Fasunex beside Nibotar at equal size ({args.design_size}): prefill and decode tok/s, bf16", "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "sizes": z,
+            "data": "synthetic: seeded random weights, seeded uniform random token ids", "models": models, "parts": parts,
+            "parts_error": errors or None, "clocks": clk.result, "peaks": pk}
+    print(json.dumps(line))
+    return 0 if all(m["finite"] for m in models.values()) else 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -623,7 +810,8 @@ def main() -> int:
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-decode", action="store_true", help="prefill only (for profiling)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
-    ap.add_argument("--design", default=None, choices=["nibotar", "tuguvik"], help="another line: this design beside Qwen3 at equal size")
+    ap.add_argument("--design", default=None, choices=["nibotar", "tuguvik", "fasunex"],
+                    help="another line: this design beside Qwen3 (fasunex: beside Nibotar) at equal size")
     ap.add_argument("--design-size", default="2k", choices=sorted(DESIGN_SIZES))
     ap.add_argument("--design-parts", nargs="?", const="both", default=None,
                     help="only the per-kernel times of --design (run by --design itself; tuguvik: of the model named)")
@@ -632,6 +820,8 @@ def main() -> int:
         return reference_arm()
     if args.design == "tuguvik":
         return tuguvik_compare(args)
+    if args.design == "fasunex":
+        return fasunex_compare(args)
     if args.design:
         return design_compare(args)
     if args.gpus != 1:
