@@ -332,12 +332,12 @@ def ssm_view(part):
                                              (2, 20, 40, 2, 2, 1), (1, 32, 300, 1, 5, 4)])
 def test_the_state_space_recurrence_in_any_portions(dtype, Hs, Pn, N, Gs, K, ng):
     g = torch.Generator().manual_seed(Hs * 1000 + N)
-    width, n = 40, 150
+    width, n = 40, 350                                       # (a step of 192 tokens or more is scanned in chunks of 64)
     m = right(Hs, Pn, N, Gs, K, ng)
     part, t = ssm_part(dtype, width, m, 1e-5, g)
     h = rnd(g, n, width)
     ref = P.state_space(as_held(h, dtype), t, "", m, 1e-5)
-    for cuts in ([n], [1] * 6 + [2, 3, 2, 59, 64, 1, 1, 12], [149, 1], [75, 75]):
+    for cuts in ([n], [1] * 6 + [2, 3, 2, 59, 64, 1, 1, 12, 200], [349, 1], [75, 75, 8, 192], [192, 158]):
         got = run_mixer(part, h, dtype, cuts, ssm_view(part))
         tight(got, ref, dtype, f"cuts {cuts[:3]}")
 

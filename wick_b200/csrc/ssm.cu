@@ -14,14 +14,32 @@
 //
 // A sequence's record (float32): [K - 1][channels] inputs of the convolution, oldest first, then the state as
 // [H][P][N] (a column of S, the N numbers that meet one element of x, lies together).  Everything here is float32
-// arithmetic; a token's numbers depend on its own sequence alone and are added in the same order whatever the step's shape
-// (a prompt in one step, in several, or token by token).
+// arithmetic; a token's numbers depend on its own sequence alone.  A step of few tokens adds them in the same order whatever
+// its shape; a long prompt step scanned in chunks (below) rounds the state differently, and no more than that.
 #include "common.cuh"
 
 namespace wick {
 
 constexpr int SSM_MAX_TAPS = 16;
 constexpr int SSM_ROWS = 16;                    // state numbers a thread keeps of one column, at most
+
+// Which tokens a block of the chunked scan takes.  A sequence's new tokens are cut into runs of `chunk` (the last one may
+// be shorter); the runs of all sequences are numbered in a row.  False beyond the last run.
+__device__ __forceinline__ bool chunk_of(int slot, int n_seqs, const int* __restrict__ cu_seqlens, int chunk, int& b, int& first,
+                                         int& len) {
+    int at = 0;
+    for (b = 0; b < n_seqs; ++b) {
+        const int t0 = cu_seqlens[b], q = cu_seqlens[b + 1] - t0, nc = (q + chunk - 1) / chunk;
+        if (slot < at + nc) {
+            const int c = slot - at;
+            first = t0 + c * chunk;
+            len = min(chunk, q - c * chunk);
+            return true;
+        }
+        at += nc;
+    }
+    return false;
+}
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
@@ -86,26 +104,40 @@ ssm_conv_state_kernel(const float* __restrict__ parts, int splits, int64_t split
     }
 }
 
-// grid (sequences * H, ceil(P / (threads / LN))).  A thread keeps `per` numbers of one column of S (the state rows
-// sub, sub + LN, ...); the LN threads of a column are neighbours in a warp.  Tokens pass in runs of `run` through shared
-// memory: x [run][cpb], B and C [run][N], dt and decay [run], y [run][cpb].
-template <int LN>
+// A thread keeps `per` numbers of one column of S (the state rows sub, sub + LN, ...); the LN threads of a column are
+// neighbours in a warp.  Tokens pass in runs of `run` through shared memory: x [run][cpb], B and C [run][N], dt and decay
+// [run], y [run][cpb].
+//   MODE 0, grid (sequences * H, ceil(P / (threads / LN))): a sequence's new tokens one after the other, from its record's
+//           state and back into it.
+// A long prompt is cut into chunks that run side by side (the recurrence is linear in the state):
+//   MODE 1, grid (chunks * H, ...): a chunk from a state of zeros; its last state goes to `chunk_state` [chunks][H][P][N] and
+//           the product of its decays to `chunk_decay` [chunks][H].  ssm_chunk_join_kernel then walks a sequence's chunks and
+//           leaves in `chunk_state` the state each chunk starts from, and the last one in the record.
+//   MODE 2, the same grid: a chunk from the state it starts from, y out.
+template <int LN, int MODE>
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __restrict__ parts, int splits, int64_t split_stride,
                 int cols, int dt_col, int H, int P, int N, int G, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state, int64_t record,
                 int64_t state_off, const int* __restrict__ slots, const int* __restrict__ cu_seqlens, float* __restrict__ y,
-                int run) {
+                int run, int n_seqs, int chunk, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
     extern __shared__ float smem[];
     pdl_trigger();
     pdl_wait();
     xbc = fresh(xbc);
     parts = fresh(parts);
     state = fresh(state);
+    chunk_state = fresh(chunk_state);
     constexpr int CPB = 128 / LN;                                        // columns a block takes
-    const int b = blockIdx.x / H, h = blockIdx.x - b * H, g = h / (H / G);
-    const int t0 = cu_seqlens[b], q = cu_seqlens[b + 1] - t0;
-    if (q <= 0) return;
+    const int unit = blockIdx.x / H, h = blockIdx.x - unit * H, g = h / (H / G);
+    int b = unit, t0, q;
+    if (MODE == 0) {
+        t0 = cu_seqlens[b];
+        q = cu_seqlens[b + 1] - t0;
+        if (q <= 0) return;
+    } else if (!chunk_of(unit, n_seqs, cu_seqlens, chunk, b, t0, q)) {
+        return;
+    }
     const int tid = threadIdx.x, sub = tid % LN, lc = tid / LN, col = blockIdx.y * CPB + lc;
     const int per = (N + LN - 1) / LN, inner = H * P;
     float* xs = smem;                                                    // [run][CPB]
@@ -114,14 +146,16 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
     float* dts = cs + run * N;                                           // [run]
     float* das = dts + run;                                              // [run]
     float* ys = das + run;                                               // [run][CPB]
-    float* sp = state + (int64_t)slots[b] * record + state_off + ((int64_t)h * P + col) * N;
+    float* sp = MODE == 0 ? state + (int64_t)slots[b] * record + state_off + ((int64_t)h * P + col) * N
+                          : chunk_state + (((int64_t)unit * H + h) * P + col) * N;
     float S[SSM_ROWS];
 #pragma unroll
     for (int r = 0; r < SSM_ROWS; ++r) {
         const int n = sub + r * LN;
-        S[r] = (r < per && n < N && col < P) ? sp[n] : 0.f;
+        S[r] = (MODE != 1 && r < per && n < N && col < P) ? sp[n] : 0.f;
     }
     const float bias = dt_bias[h], rate = -expf(a_log[h]), skip = d_skip ? d_skip[h] : 0.f;
+    float decay = 1.f;
     for (int i0 = 0; i0 < q; i0 += run) {
         const int len = min(run, q - i0);
         __syncthreads();
@@ -133,7 +167,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
             const int i = idx / N, n = idx - i * N;
             const float* rowp = xbc + (int64_t)(t0 + i0 + i) * channels + inner + g * N + n;
             bs[idx] = rowp[0];
-            cs[idx] = rowp[G * N];
+            if (MODE != 1) cs[idx] = rowp[G * N];
         }
         for (int i = tid; i < len; i += blockDim.x) {
             const float dt = softplus_f(sum_parts(parts, splits, split_stride, (int64_t)(t0 + i0 + i) * cols + dt_col + h) + bias);
@@ -141,7 +175,19 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
             das[i] = expf(rate * dt);
         }
         __syncthreads();
-        for (int i = 0; i < len; ++i) {
+        if (MODE == 1) {
+            for (int i = 0; i < len; ++i) {
+                const float xv = xs[i * CPB + lc], dt = dts[i], da = das[i];
+                const float* bi = bs + i * N;
+                decay *= da;
+#pragma unroll
+                for (int r = 0; r < SSM_ROWS; ++r) {
+                    const int n = sub + r * LN;
+                    if (r < per && n < N) S[r] = fmaf(da, S[r], (dt * bi[n]) * xv);
+                }
+            }
+        }
+        for (int i = 0; MODE != 1 && i < len; ++i) {
             const float xv = xs[i * CPB + lc], dt = dts[i], da = das[i];
             const float* bi = bs + i * N;
             const float* ci = cs + i * N;
@@ -158,12 +204,14 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
             for (int o = LN / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (sub == 0) ys[i * CPB + lc] = fmaf(skip, xv, acc);
         }
+        if (MODE == 1) continue;
         __syncthreads();
         for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
             const int i = idx / CPB, c = idx - i * CPB, pc = blockIdx.y * CPB + c;
             if (pc < P) y[(int64_t)(t0 + i0 + i) * inner + h * P + pc] = ys[idx];
         }
     }
+    if (MODE == 2) return;
     if (col < P) {
 #pragma unroll
         for (int r = 0; r < SSM_ROWS; ++r) {
@@ -171,6 +219,38 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
             if (r < per && n < N) sp[n] = S[r];
         }
     }
+    if (MODE == 1 && tid == 0 && blockIdx.y == 0) chunk_decay[(int64_t)unit * H + h] = decay;
+}
+
+// grid (sequences, ceil(H P N / 256)).  Walks a sequence's chunks in order: what a chunk starts from replaces its own last
+// state in `chunk_state`, and S <- (product of the chunk's decays) S + (the chunk's last state from zeros) goes on to the
+// next one; after the last chunk S is the record's new state.
+__global__ void __launch_bounds__(256)
+ssm_chunk_join_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay, int H, int PN, float* __restrict__ state,
+                      int64_t record, int64_t state_off, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
+                      int chunk) {
+    pdl_trigger();
+    pdl_wait();
+    chunk_state = fresh(chunk_state);
+    chunk_decay = fresh(chunk_decay);
+    state = fresh(state);
+    const int b = blockIdx.x;
+    const int64_t e = (int64_t)blockIdx.y * blockDim.x + threadIdx.x, all = (int64_t)H * PN;
+    if (e >= all) return;
+    const int q = cu_seqlens[b + 1] - cu_seqlens[b];
+    if (q <= 0) return;
+    int first = 0;
+    for (int s = 0; s < b; ++s) first += (cu_seqlens[s + 1] - cu_seqlens[s] + chunk - 1) / chunk;
+    const int nc = (q + chunk - 1) / chunk, h = (int)(e / PN);
+    float* rec = state + (int64_t)slots[b] * record + state_off + e;
+    float S = *rec;
+    for (int c = 0; c < nc; ++c) {
+        float* at = chunk_state + (int64_t)(first + c) * all + e;
+        const float local = *at;
+        *at = S;
+        S = fmaf(chunk_decay[(int64_t)(first + c) * H + h], S, local);
+    }
+    *rec = S;
 }
 
 // One block per token: g = y * silu(z) into shared memory; a warp takes whole runs (its lanes a run's elements in
@@ -201,20 +281,35 @@ ssm_gate_norm_kernel(const float* __restrict__ y, const float* __restrict__ part
     for (int j = tid; j < inner; j += blockDim.x) st(out + (int64_t)t * inner + j, (row[j] * factor[j / len]) * w[j]);
 }
 
-template <int LN>
-int scan_launch(int n_seqs, int H, int P, int N, size_t smem, cudaStream_t s, const float* xbc, int channels, const float* parts,
-                int splits, int64_t split_stride, int cols, int dt_col, int G, const float* dt_bias, const float* a_log,
-                const float* d_skip, float* state, int64_t record, int64_t state_off, const int* slots, const int* cu_seqlens,
-                float* y, int run) {
+struct ScanArgs {
+    const float* xbc; int channels; const float* parts; int splits; int64_t split_stride; int cols, dt_col, H, P, N, G;
+    const float *dt_bias, *a_log, *d_skip; float* state; int64_t record, state_off; const int *slots, *cu_seqlens; float* y;
+    int run, n_seqs, chunk; float *chunk_state, *chunk_decay;
+};
+
+template <int LN, int MODE>
+int scan_launch_mode(const ScanArgs& a, int units, size_t smem, cudaStream_t s) {
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        WICK_CUDA(cudaFuncSetAttribute(ssm_scan_kernel<LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        WICK_CUDA(cudaFuncSetAttribute(ssm_scan_kernel<LN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         raised = true;
     }
-    WICK_CUDA(launch(ssm_scan_kernel<LN>, dim3(n_seqs * H, ceil_div(P, 128 / LN)), dim3(128), smem, s, xbc, channels, parts, splits,
-                     split_stride, cols, dt_col, H, P, N, G, dt_bias, a_log, d_skip, state, record, state_off, slots, cu_seqlens, y,
-                     run));
+    WICK_CUDA(launch(ssm_scan_kernel<LN, MODE>, dim3(units * a.H, ceil_div(a.P, 128 / LN)), dim3(128), smem, s, a.xbc, a.channels,
+                     a.parts, a.splits, a.split_stride, a.cols, a.dt_col, a.H, a.P, a.N, a.G, a.dt_bias, a.a_log, a.d_skip, a.state,
+                     a.record, a.state_off, a.slots, a.cu_seqlens, a.y, a.run, a.n_seqs, a.chunk, a.chunk_state, a.chunk_decay));
     return check_launch("ssm_scan");
+}
+
+// chunks == 0: every sequence's tokens one after the other; else the three steps of the chunked scan over `chunks` units.
+template <int LN>
+int scan_launch(const ScanArgs& a, int chunks, size_t smem, cudaStream_t s) {
+    if (chunks == 0) return scan_launch_mode<LN, 0>(a, a.n_seqs, smem, s);
+    if (scan_launch_mode<LN, 1>(a, chunks, smem, s)) return 1;
+    const int64_t all = (int64_t)a.H * a.P * a.N;
+    WICK_CUDA(launch(ssm_chunk_join_kernel, dim3(a.n_seqs, (unsigned)ceil_div(all, (int64_t)256)), dim3(256), 0, s, a.chunk_state,
+                     (const float*)a.chunk_decay, a.H, a.P * a.N, a.state, a.record, a.state_off, a.slots, a.cu_seqlens, a.chunk));
+    if (check_launch("ssm_chunk_join")) return 1;
+    return scan_launch_mode<LN, 2>(a, chunks, smem, s);
 }
 
 }  // namespace wick
@@ -223,11 +318,14 @@ using namespace wick;
 typedef __nv_bfloat16 bf16;
 
 // parts: float32 [splits, n, cols] laid out [z | x | B | C | dt]; state: float32 [slots, record]; xbc: float32
-// [n, channels] and y: float32 [n, H P], both written here.  max_q: the most tokens a sequence can bring.
+// [n, channels] and y: float32 [n, H P], both written here.  max_q: the most tokens a sequence can bring (0: unknown).
+// chunks > 0: the sequences' tokens are scanned in chunks of `chunk` tokens side by side; `chunks` is at least the number of
+// chunks (n / chunk + n_seqs is enough), chunk_state float32 [chunks, H P N] and chunk_decay float32 [chunks, H] are scratch.
 WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H, int P, int N, int G, int taps, const float* conv_w,
                           const float* conv_b, const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                           int64_t record, const int* slots, int n_seqs, const int* cu_seqlens, const int* start,
-                          const int* seq_of_token, const int* positions, float* xbc, float* y, int max_q, void* stream) {
+                          const int* seq_of_token, const int* positions, float* xbc, float* y, int max_q, int chunk, int chunks,
+                          float* chunk_state, float* chunk_decay, void* stream) {
     cudaStream_t s = (cudaStream_t)stream;
     WICK_REQUIRE(H > 0 && P > 0 && N > 0 && G > 0 && H % G == 0, "ssm_mix: bad sizes");
     WICK_REQUIRE(taps >= 1 && taps <= SSM_MAX_TAPS, "ssm_mix: %d taps (1 .. %d are built)", taps, SSM_MAX_TAPS);
@@ -236,6 +334,8 @@ WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H
     WICK_REQUIRE(cols == 2 * inner + 2 * G * N + H, "ssm_mix: rows of %d numbers, %d expected", cols, 2 * inner + 2 * G * N + H);
     WICK_REQUIRE(record == (int64_t)(taps - 1) * channels + (int64_t)H * P * N, "ssm_mix: records of another size");
     WICK_REQUIRE(splits >= 1, "ssm_mix: partial sums are needed");
+    WICK_REQUIRE(chunks == 0 || (chunk > 0 && chunk_state && chunk_decay && (int64_t)chunks >= n / chunk + n_seqs),
+                 "ssm_mix: the chunked scan needs room for %d chunks", chunk > 0 ? n / chunk + n_seqs : 0);
     if (n == 0 || n_seqs == 0) return 0;
     const int64_t stride = (int64_t)n * cols;
     WICK_CUDA(launch(ssm_conv_kernel, dim3(n, ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride, cols, inner, channels,
@@ -253,21 +353,19 @@ WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H
     int run = (40 * 1024 / 4) / (2 * cpb + 2 * N + 2);
     run = run < 1 ? 1 : (run > 64 ? 64 : run);
     if (run > max_q && max_q >= 1) run = max_q;
+    if (chunks > 0 && run > chunk) run = chunk;
+    if (chunks > 0 && run < chunk && run > chunk / 2) run = chunk / 2;      // (equal runs)
     const size_t smem = (size_t)run * (2 * cpb + 2 * N + 2) * sizeof(float);
-    const int64_t state_off = (int64_t)(taps - 1) * channels;
-#define WICK_SCAN(LN)                                                                                                          \
-    return scan_launch<LN>(n_seqs, H, P, N, smem, s, xbc, channels, parts, splits, stride, cols, 2 * inner + 2 * G * N, G, dt_bias, \
-                           a_log, d_skip, state, record, state_off, slots, cu_seqlens, y, run)
+    const ScanArgs a = {xbc, channels, parts, splits, stride, cols, 2 * inner + 2 * G * N, H, P, N, G, dt_bias, a_log, d_skip, state,
+                        record, (int64_t)(taps - 1) * channels, slots, cu_seqlens, y, run, n_seqs, chunk, chunk_state, chunk_decay};
     switch (ln) {
-        case 1: WICK_SCAN(1);
-        case 2: WICK_SCAN(2);
-        case 4: WICK_SCAN(4);
-        case 8: WICK_SCAN(8);
-        case 16: WICK_SCAN(16);
-        default: WICK_SCAN(32);
+        case 1: return scan_launch<1>(a, chunks, smem, s);
+        case 2: return scan_launch<2>(a, chunks, smem, s);
+        case 4: return scan_launch<4>(a, chunks, smem, s);
+        case 8: return scan_launch<8>(a, chunks, smem, s);
+        case 16: return scan_launch<16>(a, chunks, smem, s);
+        default: return scan_launch<32>(a, chunks, smem, s);
     }
-#undef WICK_SCAN
-    return 0;
 }
 
 // y: float32 [n, inner]; parts as above (z in its first columns); w: float32 [inner]; out: [n, inner].

@@ -1191,6 +1191,10 @@ def ssm_record_floats(heads: int, head_dim: int, state: int, groups: int, taps: 
     return (taps - 1) * (heads * head_dim + 2 * groups * state) + heads * head_dim * state
 
 
+SSM_CHUNK = 64            # tokens of one chunk of a long prompt's scan
+SSM_CHUNKED_FROM = 192    # a prompt step of this many tokens or more is scanned in chunks
+
+
 def ssm_mix(parts: torch.Tensor, *, heads: int, head_dim: int, state: int, groups: int, taps: int, conv_w: torch.Tensor,
             conv_b: Optional[torch.Tensor], dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: Optional[torch.Tensor],
             records: torch.Tensor, batch) -> torch.Tensor:
@@ -1218,10 +1222,18 @@ def ssm_mix(parts: torch.Tensor, *, heads: int, head_dim: int, state: int, group
     xbc = torch.empty((n, channels), dtype=torch.float32, device=parts.device)
     y = torch.empty((n, inner), dtype=torch.float32, device=parts.device)
     max_q = 1 if batch.is_decode else 0          # (0: unknown to the host, as in a captured prompt step)
-    _layer().call("wick_ssm_mix", "piiiiiiiipppppplpippppppip", _p(parts), splits, n, cols, heads, head_dim, state, groups, taps,
+    # A prompt step of many tokens is scanned in chunks side by side (three kernels instead of one); what the chunks' states
+    # need is scratch of this call.
+    chunk, chunks, chunk_state, chunk_decay = SSM_CHUNK, 0, None, None
+    if not batch.is_decode and n >= SSM_CHUNKED_FROM:
+        chunks = n // chunk + batch.n_seqs
+        chunk_state = torch.empty((chunks, inner * state), dtype=torch.float32, device=parts.device)
+        chunk_decay = torch.empty((chunks, heads), dtype=torch.float32, device=parts.device)
+    _layer().call("wick_ssm_mix", "piiiiiiiipppppplpippppppiiippp", _p(parts), splits, n, cols, heads, head_dim, state, groups, taps,
                   _p(conv_w), _p(conv_b), _p(dt_bias), _p(a_log), _p(d_skip), _p(records), record, _p(batch.slots), batch.n_seqs,
                   _p(batch.cu_seqlens), _p(batch.start), _p(batch.seq_of_token), _p(batch.positions), _p(xbc), _p(y), max_q,
-                  _stream(), kernels=3 if taps > 1 else 2)
+                  chunk, chunks, _p(chunk_state), _p(chunk_decay), _stream(),
+                  kernels=(2 if taps > 1 else 1) + (3 if chunks else 1))
     return y
 
 
