@@ -22,6 +22,7 @@ namespace wick {
 
 constexpr int SSM_MAX_TAPS = 16;
 constexpr int SSM_ROWS = 16;                    // state numbers a thread keeps of one column, at most
+constexpr int SSM_COLS = 4;                     // columns of the state a thread keeps
 
 // Which tokens a block of the chunked scan takes.  A sequence's new tokens are cut into runs of `chunk` (the last one may
 // be shorter); the runs of all sequences are numbered in a row.  False beyond the last run.
@@ -40,6 +41,16 @@ __device__ __forceinline__ bool chunk_of(int slot, int n_seqs, const int* __rest
     }
     return false;
 }
+
+// Asynchronous copies of BYTES (4 or 16) from global into shared memory, in groups a thread waits for.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(d), "l"(src), "n"(BYTES) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory"); }
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
@@ -104,11 +115,40 @@ ssm_conv_state_kernel(const float* __restrict__ parts, int splits, int64_t split
     }
 }
 
-// A thread keeps `per` numbers of one column of S (the state rows sub, sub + LN, ...); the LN threads of a column are
-// neighbours in a warp.  Tokens pass in runs of `run` through shared memory: x [run][cpb], B and C [run][N], dt and decay
-// [run], y [run][cpb].
-//   MODE 0, grid (sequences * H, ceil(P / (threads / LN))): a sequence's new tokens one after the other, from its record's
-//           state and back into it.
+// The sums of four columns over the LN threads that share them.  Two exchanges halve what a thread carries (it keeps two
+// columns, then one), the rest is a butterfly over one number; `col` is the column a thread ends with and `writes` whether
+// it is the one of its group that holds it (LN < 4: every column stays, a[0..3] hold the sums).
+template <int LN>
+__device__ __forceinline__ float sum_columns(float (&a)[4], int sub, int& col, bool& writes) {
+    constexpr unsigned ALL = 0xffffffffu;
+    if (LN < 4) {
+#pragma unroll
+        for (int o = LN / 2; o > 0; o >>= 1)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) a[c] += __shfl_xor_sync(ALL, a[c], o);
+        col = -1;
+        writes = sub == 0;
+        return 0.f;
+    }
+    constexpr int O1 = LN >= 4 ? LN / 2 : 1, O2 = LN >= 4 ? LN / 4 : 1;
+    const bool hi = (sub & O1) != 0, hi2 = (sub & O2) != 0;
+    const float k0 = (hi ? a[2] : a[0]) + __shfl_xor_sync(ALL, hi ? a[0] : a[2], O1);
+    const float k1 = (hi ? a[3] : a[1]) + __shfl_xor_sync(ALL, hi ? a[1] : a[3], O1);
+    float m = (hi2 ? k1 : k0) + __shfl_xor_sync(ALL, hi2 ? k0 : k1, O2);
+#pragma unroll
+    for (int o = LN / 8; o > 0; o >>= 1) m += __shfl_xor_sync(ALL, m, o);
+    col = (hi ? 2 : 0) + (hi2 ? 1 : 0);
+    writes = (sub & (O2 - 1)) == 0;
+    return m;
+}
+
+// A thread keeps a tile of S in registers: SSM_COLS columns (elements of x) by up to SSM_ROWS state rows, the rows in groups
+// of four neighbours, group r of thread `sub` being the rows (r LN + sub) 4 .. + 3; the LN threads that share four columns
+// are neighbours in a warp.  Tokens pass in runs of `run` through shared memory: x [run][cpb], B and C [run][NP] (NP: N
+// rounded up to whole groups, zeros beyond N, so that the loop tests nothing), y [run][cpb], dt and decay [run]; a thread
+// reads them as vectors of four.
+//   MODE 0, grid (sequences * H, ceil(P / cpb)): a sequence's new tokens one after the other, from its record's state and
+//           back into it.
 // A long prompt is cut into chunks that run side by side (the recurrence is linear in the state):
 //   MODE 1, grid (chunks * H, ...): a chunk from a state of zeros; its last state goes to `chunk_state` [chunks][H][P][N] and
 //           the product of its decays to `chunk_decay` [chunks][H].  ssm_chunk_join_kernel then walks a sequence's chunks and
@@ -121,14 +161,16 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
                 const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state, int64_t record,
                 int64_t state_off, const int* __restrict__ slots, const int* __restrict__ cu_seqlens, float* __restrict__ y,
                 int run, int n_seqs, int chunk, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
-    extern __shared__ float smem[];
+    extern __shared__ float4 smem4[];
+    float* smem = reinterpret_cast<float*>(smem4);
     pdl_trigger();
     pdl_wait();
     xbc = fresh(xbc);
     parts = fresh(parts);
     state = fresh(state);
     chunk_state = fresh(chunk_state);
-    constexpr int CPB = 128 / LN;                                        // columns a block takes
+    constexpr int CT = SSM_COLS, R4 = SSM_ROWS / 4;
+    const int CPB = (int)blockDim.x / LN * CT;                          // columns a block takes
     const int unit = blockIdx.x / H, h = blockIdx.x - unit * H, g = h / (H / G);
     int b = unit, t0, q;
     if (MODE == 0) {
@@ -138,87 +180,185 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const float* __rest
     } else if (!chunk_of(unit, n_seqs, cu_seqlens, chunk, b, t0, q)) {
         return;
     }
-    const int tid = threadIdx.x, sub = tid % LN, lc = tid / LN, col = blockIdx.y * CPB + lc;
-    const int per = (N + LN - 1) / LN, inner = H * P;
-    float* xs = smem;                                                    // [run][CPB]
-    float* bs = xs + run * CPB;                                          // [run][N]
-    float* cs = bs + run * N;                                            // [run][N]
-    float* dts = cs + run * N;                                           // [run]
-    float* das = dts + run;                                              // [run]
-    float* ys = das + run;                                               // [run][CPB]
-    float* sp = MODE == 0 ? state + (int64_t)slots[b] * record + state_off + ((int64_t)h * P + col) * N
-                          : chunk_state + (((int64_t)unit * H + h) * P + col) * N;
-    float S[SSM_ROWS];
+    const int tid = threadIdx.x, sub = tid % LN, lc = tid / LN, pc0 = blockIdx.y * CPB, col0 = pc0 + lc * CT;
+    const int per4 = (N + 4 * LN - 1) / (4 * LN), NP = per4 * 4 * LN, inner = H * P;
+    // Two stages of a run's inputs (the next run is copied while this one is computed), then the run's results.
+    const int stage = (run * (CPB + 2 * NP + 2) + 3) & ~3;
+    float* ys = smem + 2 * stage;                                        // [run][CPB]
+    float* sp = MODE == 0 ? state + (int64_t)slots[b] * record + state_off + ((int64_t)h * P + col0) * N
+                          : chunk_state + (((int64_t)unit * H + h) * P + col0) * N;
+    const bool whole = (N & 3) == 0 && (reinterpret_cast<size_t>(sp) & 15) == 0;     // (a group of rows is one aligned vector)
+    // (rows of x, B, C and y start on 16-byte borders: they are copied as vectors of four)
+    const bool vec = ((channels | P | N) & 3) == 0 && ((reinterpret_cast<size_t>(xbc) | reinterpret_cast<size_t>(y)) & 15) == 0;
+    float S[R4][4][CT];
 #pragma unroll
-    for (int r = 0; r < SSM_ROWS; ++r) {
-        const int n = sub + r * LN;
-        S[r] = (MODE != 1 && r < per && n < N && col < P) ? sp[n] : 0.f;
-    }
+    for (int r = 0; r < R4; ++r)
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            const int n = (r * LN + sub) * 4;
+            const bool in = MODE != 1 && r < per4 && col0 + c < P;
+            if (in && whole && n < N) {
+                const float4 v = *reinterpret_cast<const float4*>(sp + (int64_t)c * N + n);
+                S[r][0][c] = v.x, S[r][1][c] = v.y, S[r][2][c] = v.z, S[r][3][c] = v.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) S[r][j][c] = (in && n + j < N) ? sp[(int64_t)c * N + n + j] : 0.f;
+            }
+        }
     const float bias = dt_bias[h], rate = -expf(a_log[h]), skip = d_skip ? d_skip[h] : 0.f;
+    // What lies beyond the head's columns and the state's rows stays zero in both stages: the copies never write there.
+    if (NP != N || pc0 + CPB > P) {
+        for (int idx = tid; idx < 2 * stage; idx += blockDim.x) smem[idx] = 0.f;
+        __syncthreads();
+    }
+    // Copies the inputs of the run that starts at token i0 into stage `st` (asynchronously, one group).
+    auto copy_run = [&](int st, int i0, int len) {
+        float* xs = smem + st * stage;                                   // [run][CPB]
+        float* bs = xs + run * CPB;                                      // [run][NP]
+        float* cs = bs + run * NP;                                       // [run][NP]
+        const float* src = xbc + (int64_t)(t0 + i0) * channels;
+        if (vec) {
+            const int c4 = CPB / 4, n4 = NP / 4;
+            for (int idx = tid; idx < len * c4; idx += blockDim.x) {
+                const int i = idx / c4, c = (idx - i * c4) * 4;
+                if (pc0 + c < P) cp_async<16>(xs + i * CPB + c, src + (int64_t)i * channels + h * P + pc0 + c);
+            }
+            for (int idx = tid; idx < len * n4; idx += blockDim.x) {
+                const int i = idx / n4, n = (idx - i * n4) * 4;
+                if (n < N) {
+                    const float* rowp = src + (int64_t)i * channels + inner + g * N + n;
+                    cp_async<16>(bs + i * NP + n, rowp);
+                    if (MODE != 1) cp_async<16>(cs + i * NP + n, rowp + G * N);
+                }
+            }
+        } else {
+            for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
+                const int i = idx / CPB, c = idx - i * CPB;
+                if (pc0 + c < P) cp_async<4>(xs + idx, src + (int64_t)i * channels + h * P + pc0 + c);
+            }
+            for (int idx = tid; idx < len * NP; idx += blockDim.x) {
+                const int i = idx / NP, n = idx - i * NP;
+                if (n < N) {
+                    const float* rowp = src + (int64_t)i * channels + inner + g * N + n;
+                    cp_async<4>(bs + idx, rowp);
+                    if (MODE != 1) cp_async<4>(cs + idx, rowp + G * N);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+    // A run's step sizes: read early (raw), turned into dt and the decay and stored late; two a thread at most (run <= 64).
+    auto raw_steps = [&](int i0, int len, float (&raw)[2]) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = tid + k * blockDim.x;
+            raw[k] = i < len ? sum_parts(parts, splits, split_stride, (int64_t)(t0 + i0 + i) * cols + dt_col + h) : 0.f;
+        }
+    };
+    auto store_steps = [&](int st, int len, const float (&raw)[2]) {
+        float* dts = smem + st * stage + run * (CPB + 2 * NP);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = tid + k * blockDim.x;
+            if (i < len) {
+                const float dt = softplus_f(raw[k] + bias);
+                dts[i] = dt;
+                dts[run + i] = expf(rate * dt);
+            }
+        }
+    };
     float decay = 1.f;
-    for (int i0 = 0; i0 < q; i0 += run) {
-        const int len = min(run, q - i0);
-        __syncthreads();
-        for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
-            const int i = idx / CPB, c = idx - i * CPB, pc = blockIdx.y * CPB + c;
-            xs[idx] = pc < P ? xbc[(int64_t)(t0 + i0 + i) * channels + h * P + pc] : 0.f;
-        }
-        for (int idx = tid; idx < len * N; idx += blockDim.x) {
-            const int i = idx / N, n = idx - i * N;
-            const float* rowp = xbc + (int64_t)(t0 + i0 + i) * channels + inner + g * N + n;
-            bs[idx] = rowp[0];
-            if (MODE != 1) cs[idx] = rowp[G * N];
-        }
-        for (int i = tid; i < len; i += blockDim.x) {
-            const float dt = softplus_f(sum_parts(parts, splits, split_stride, (int64_t)(t0 + i0 + i) * cols + dt_col + h) + bias);
-            dts[i] = dt;
-            das[i] = expf(rate * dt);
+    float raw[2];
+    copy_run(0, 0, min(run, q));
+    raw_steps(0, min(run, q), raw);
+    store_steps(0, min(run, q), raw);
+    for (int i0 = 0, st = 0; i0 < q; i0 += run, st ^= 1) {
+        const int len = min(run, q - i0), next = min(run, q - i0 - run);
+        if (next > 0) {
+            copy_run(st ^ 1, i0 + run, next);
+            raw_steps(i0 + run, next, raw);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
-        if (MODE == 1) {
-            for (int i = 0; i < len; ++i) {
-                const float xv = xs[i * CPB + lc], dt = dts[i], da = das[i];
-                const float* bi = bs + i * N;
-                decay *= da;
+        const float* xs = smem + st * stage;
+        const float* bs = xs + run * CPB;
+        const float* cs = bs + run * NP;
+        const float* dts = cs + run * NP;
+        const float* das = dts + run;
+        for (int i = 0; i < len; ++i) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + i * CPB + lc * CT);
+            const float dt = dts[i], da = das[i];
+            const float x[CT] = {xv.x, xv.y, xv.z, xv.w};
+            const float4* bi = reinterpret_cast<const float4*>(bs + i * NP) + sub;
+            const float4* ci = reinterpret_cast<const float4*>(cs + i * NP) + sub;
+            float acc[CT] = {0.f, 0.f, 0.f, 0.f};
+            if (MODE == 1) decay *= da;
 #pragma unroll
-                for (int r = 0; r < SSM_ROWS; ++r) {
-                    const int n = sub + r * LN;
-                    if (r < per && n < N) S[r] = fmaf(da, S[r], (dt * bi[n]) * xv);
+            for (int r = 0; r < R4; ++r) {
+                if (r < per4) {
+                    const float4 bv = bi[r * LN];
+                    const float bd[4] = {dt * bv.x, dt * bv.y, dt * bv.z, dt * bv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int c = 0; c < CT; ++c) S[r][j][c] = fmaf(da, S[r][j][c], bd[j] * x[c]);
+                    if (MODE != 1) {
+                        const float4 cv = ci[r * LN];
+                        const float cc[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int c = 0; c < CT; ++c) acc[c] = fmaf(S[r][j][c], cc[j], acc[c]);
+                    }
+                }
+            }
+            if (MODE != 1) {
+                int c1;
+                bool writes;
+                const float m = sum_columns<LN>(acc, sub, c1, writes);
+                float* yi = ys + i * CPB + lc * CT;
+                if (LN < 4) {
+                    if (writes) *reinterpret_cast<float4*>(yi) = make_float4(fmaf(skip, x[0], acc[0]), fmaf(skip, x[1], acc[1]),
+                                                                             fmaf(skip, x[2], acc[2]), fmaf(skip, x[3], acc[3]));
+                } else if (writes) {
+                    yi[c1] = fmaf(skip, c1 == 0 ? x[0] : c1 == 1 ? x[1] : c1 == 2 ? x[2] : x[3], m);
                 }
             }
         }
-        for (int i = 0; MODE != 1 && i < len; ++i) {
-            const float xv = xs[i * CPB + lc], dt = dts[i], da = das[i];
-            const float* bi = bs + i * N;
-            const float* ci = cs + i * N;
-            float acc = 0.f;
-#pragma unroll
-            for (int r = 0; r < SSM_ROWS; ++r) {
-                const int n = sub + r * LN;
-                if (r < per && n < N) {
-                    S[r] = fmaf(da, S[r], (dt * bi[n]) * xv);
-                    acc = fmaf(S[r], ci[n], acc);
-                }
-            }
-#pragma unroll
-            for (int o = LN / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (sub == 0) ys[i * CPB + lc] = fmaf(skip, xv, acc);
-        }
+        if (next > 0) store_steps(st ^ 1, next, raw);
+        __syncthreads();                                 // (the run's results are whole; nobody reads this stage any more)
         if (MODE == 1) continue;
-        __syncthreads();
-        for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
-            const int i = idx / CPB, c = idx - i * CPB, pc = blockIdx.y * CPB + c;
-            if (pc < P) y[(int64_t)(t0 + i0 + i) * inner + h * P + pc] = ys[idx];
+        float* dst = y + (int64_t)(t0 + i0) * inner + h * P + pc0;
+        if (vec) {
+            const int c4 = CPB / 4;
+            for (int idx = tid; idx < len * c4; idx += blockDim.x) {
+                const int i = idx / c4, c = (idx - i * c4) * 4;
+                if (pc0 + c < P) *reinterpret_cast<float4*>(dst + (int64_t)i * inner + c) = *reinterpret_cast<const float4*>(ys + i * CPB + c);
+            }
+        } else {
+            for (int idx = tid; idx < len * CPB; idx += blockDim.x) {
+                const int i = idx / CPB, c = idx - i * CPB;
+                if (pc0 + c < P) dst[(int64_t)i * inner + c] = ys[idx];
+            }
         }
     }
     if (MODE == 2) return;
-    if (col < P) {
 #pragma unroll
-        for (int r = 0; r < SSM_ROWS; ++r) {
-            const int n = sub + r * LN;
-            if (r < per && n < N) sp[n] = S[r];
+    for (int r = 0; r < R4; ++r)
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            const int n = (r * LN + sub) * 4;
+            if (r >= per4 || col0 + c >= P) continue;
+            if (whole && n < N) {
+                *reinterpret_cast<float4*>(sp + (int64_t)c * N + n) = make_float4(S[r][0][c], S[r][1][c], S[r][2][c], S[r][3][c]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (n + j < N) sp[(int64_t)c * N + n + j] = S[r][j][c];
+            }
         }
-    }
     if (MODE == 1 && tid == 0 && blockIdx.y == 0) chunk_decay[(int64_t)unit * H + h] = decay;
 }
 
@@ -244,11 +384,19 @@ ssm_chunk_join_kernel(float* __restrict__ chunk_state, const float* __restrict__
     const int nc = (q + chunk - 1) / chunk, h = (int)(e / PN);
     float* rec = state + (int64_t)slots[b] * record + state_off + e;
     float S = *rec;
-    for (int c = 0; c < nc; ++c) {
-        float* at = chunk_state + (int64_t)(first + c) * all + e;
-        const float local = *at;
-        *at = S;
-        S = fmaf(chunk_decay[(int64_t)(first + c) * H + h], S, local);
+    for (int c0 = 0; c0 < nc; c0 += 8) {                                 // (eight chunks' numbers are on their way at once)
+        float local[8], dec[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool in = c0 + k < nc;
+            local[k] = in ? chunk_state[(int64_t)(first + c0 + k) * all + e] : 0.f;
+            dec[k] = in ? chunk_decay[(int64_t)(first + c0 + k) * H + h] : 1.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < nc) chunk_state[(int64_t)(first + c0 + k) * all + e] = S;
+            S = fmaf(dec[k], S, local[k]);
+        }
     }
     *rec = S;
 }
@@ -284,7 +432,7 @@ ssm_gate_norm_kernel(const float* __restrict__ y, const float* __restrict__ part
 struct ScanArgs {
     const float* xbc; int channels; const float* parts; int splits; int64_t split_stride; int cols, dt_col, H, P, N, G;
     const float *dt_bias, *a_log, *d_skip; float* state; int64_t record, state_off; const int *slots, *cu_seqlens; float* y;
-    int run, n_seqs, chunk; float *chunk_state, *chunk_decay;
+    int run, n_seqs, chunk; float *chunk_state, *chunk_decay; int threads;
 };
 
 template <int LN, int MODE>
@@ -294,7 +442,7 @@ int scan_launch_mode(const ScanArgs& a, int units, size_t smem, cudaStream_t s) 
         WICK_CUDA(cudaFuncSetAttribute(ssm_scan_kernel<LN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         raised = true;
     }
-    WICK_CUDA(launch(ssm_scan_kernel<LN, MODE>, dim3(units * a.H, ceil_div(a.P, 128 / LN)), dim3(128), smem, s, a.xbc, a.channels,
+    WICK_CUDA(launch(ssm_scan_kernel<LN, MODE>, dim3(units * a.H, ceil_div(a.P, a.threads / LN * SSM_COLS)), dim3(a.threads), smem, s, a.xbc, a.channels,
                      a.parts, a.splits, a.split_stride, a.cols, a.dt_col, a.H, a.P, a.N, a.G, a.dt_bias, a.a_log, a.d_skip, a.state,
                      a.record, a.state_off, a.slots, a.cu_seqlens, a.y, a.run, a.n_seqs, a.chunk, a.chunk_state, a.chunk_decay));
     return check_launch("ssm_scan");
@@ -349,15 +497,20 @@ WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H
     int ln = 1;
     while (ln < 32 && (N + ln - 1) / ln > SSM_ROWS) ln *= 2;
     if (ln < 4 && N >= 16) ln = 4;                                       // (a thread keeps a few numbers, not a whole column)
-    const int cpb = 128 / ln;
-    int run = (40 * 1024 / 4) / (2 * cpb + 2 * N + 2);
+    // A block: as many threads as the head's columns need (whole warps, 128 at most), each group of `ln` taking SSM_COLS columns.
+    int threads = ceil_div(P, SSM_COLS) * ln;
+    threads = threads > 128 ? 128 : (threads + 31) / 32 * 32;
+    const int cpb = threads / ln * SSM_COLS, np = ceil_div(N, 4 * ln) * 4 * ln;
+    const int per_token = 2 * (cpb + 2 * np + 2) + cpb;                   // (two stages of inputs, one of results)
+    int run = (52 * 1024 / 4) / per_token;                                // (four blocks of this size share an SM)
     run = run < 1 ? 1 : (run > 64 ? 64 : run);
     if (run > max_q && max_q >= 1) run = max_q;
     if (chunks > 0 && run > chunk) run = chunk;
-    if (chunks > 0 && run < chunk && run > chunk / 2) run = chunk / 2;      // (equal runs)
-    const size_t smem = (size_t)run * (2 * cpb + 2 * N + 2) * sizeof(float);
+    if (chunks > 0 && run < chunk) run = ceil_div(chunk, ceil_div(chunk, run));   // (equal runs)
+    const size_t smem = (size_t)(2 * ((run * (cpb + 2 * np + 2) + 3) & ~3) + run * cpb) * sizeof(float);
     const ScanArgs a = {xbc, channels, parts, splits, stride, cols, 2 * inner + 2 * G * N, H, P, N, G, dt_bias, a_log, d_skip, state,
-                        record, (int64_t)(taps - 1) * channels, slots, cu_seqlens, y, run, n_seqs, chunk, chunk_state, chunk_decay};
+                        record, (int64_t)(taps - 1) * channels, slots, cu_seqlens, y, run, n_seqs, chunk, chunk_state, chunk_decay,
+                        threads};
     switch (ln) {
         case 1: return scan_launch<1>(a, chunks, smem, s);
         case 2: return scan_launch<2>(a, chunks, smem, s);
