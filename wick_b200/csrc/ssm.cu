@@ -61,29 +61,50 @@ __device__ __forceinline__ float sum_parts(const float* __restrict__ parts, int 
     return v;
 }
 
-// grid (tokens, ceil(channels / 256)).
+constexpr int SSM_CONV_TOKENS = 4;              // tokens a thread of the convolution takes (their loads are in flight together)
+
+// grid (ceil(tokens / SSM_CONV_TOKENS), ceil(channels / 256)).
 __global__ void __launch_bounds__(256)
 ssm_conv_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int cols, int first_col, int channels, int taps,
                 const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state, int64_t record,
                 const int* __restrict__ slots, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                const int* __restrict__ start, float* __restrict__ out) {
+                const int* __restrict__ start, float* __restrict__ out, int n) {
     pdl_trigger();
     pdl_wait();
     parts = fresh(parts);
     state = fresh(state);
-    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= channels) return;
-    const int b = seq_of_token[t], pos = positions[t], first = start[b];
-    const float* rec = state + (int64_t)slots[b] * record;
-    float acc = bias ? bias[c] : 0.f;
-    for (int k = 0; k < taps; ++k) {
-        const int sp = pos - (taps - 1) + k;
-        float u = 0.f;
-        if (sp >= first) u = sum_parts(parts, splits, split_stride, (int64_t)(t - (pos - sp)) * cols + first_col + c);
-        else if (sp >= 0) u = rec[(int64_t)(sp - (first - (taps - 1))) * channels + c];
-        acc = fmaf(w[(int64_t)c * taps + k], u, acc);
+    const float b0 = bias ? bias[c] : 0.f;
+    float acc[SSM_CONV_TOKENS];
+    int pos[SSM_CONV_TOKENS], first[SSM_CONV_TOKENS];
+    const float* rec[SSM_CONV_TOKENS];
+#pragma unroll
+    for (int j = 0; j < SSM_CONV_TOKENS; ++j) {
+        const int t = min(blockIdx.x * SSM_CONV_TOKENS + j, n - 1), b = seq_of_token[t];
+        pos[j] = positions[t];
+        first[j] = start[b];
+        rec[j] = state + (int64_t)slots[b] * record;
+        acc[j] = b0;
     }
-    out[(int64_t)t * channels + c] = silu_f(acc);
+    for (int k = 0; k < taps; ++k) {
+        const float wk = w[(int64_t)c * taps + k];
+        float u[SSM_CONV_TOKENS];
+#pragma unroll
+        for (int j = 0; j < SSM_CONV_TOKENS; ++j) {
+            const int t = min(blockIdx.x * SSM_CONV_TOKENS + j, n - 1), sp = pos[j] - (taps - 1) + k;
+            u[j] = 0.f;
+            if (sp >= first[j]) u[j] = sum_parts(parts, splits, split_stride, (int64_t)(t - (pos[j] - sp)) * cols + first_col + c);
+            else if (sp >= 0) u[j] = rec[j][(int64_t)(sp - (first[j] - (taps - 1))) * channels + c];
+        }
+#pragma unroll
+        for (int j = 0; j < SSM_CONV_TOKENS; ++j) acc[j] = fmaf(wk, u[j], acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < SSM_CONV_TOKENS; ++j) {
+        const int t = blockIdx.x * SSM_CONV_TOKENS + j;
+        if (t < n) out[(int64_t)t * channels + c] = silu_f(acc[j]);
+    }
 }
 
 // grid (sequences, ceil(channels / 256)).  Runs after the convolution has read the old inputs.
@@ -486,8 +507,9 @@ WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H
                  "ssm_mix: the chunked scan needs room for %d chunks", chunk > 0 ? n / chunk + n_seqs : 0);
     if (n == 0 || n_seqs == 0) return 0;
     const int64_t stride = (int64_t)n * cols;
-    WICK_CUDA(launch(ssm_conv_kernel, dim3(n, ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride, cols, inner, channels,
-                     taps, conv_w, conv_b, (const float*)state, record, slots, seq_of_token, positions, start, xbc));
+    WICK_CUDA(launch(ssm_conv_kernel, dim3(ceil_div(n, SSM_CONV_TOKENS), ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride,
+                     cols, inner, channels, taps, conv_w, conv_b, (const float*)state, record, slots, seq_of_token, positions, start,
+                     xbc, n));
     if (check_launch("ssm_conv")) return 1;
     if (taps > 1) {
         WICK_CUDA(launch(ssm_conv_state_kernel, dim3(n_seqs, ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride, cols,
