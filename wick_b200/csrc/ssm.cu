@@ -498,6 +498,7 @@ WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H
     cudaStream_t s = (cudaStream_t)stream;
     WICK_REQUIRE(H > 0 && P > 0 && N > 0 && G > 0 && H % G == 0, "ssm_mix: bad sizes");
     WICK_REQUIRE(taps >= 1 && taps <= SSM_MAX_TAPS, "ssm_mix: %d taps (1 .. %d are built)", taps, SSM_MAX_TAPS);
+    WICK_REQUIRE(N <= SSM_ROWS * 32, "ssm_mix: a state of %d rows (up to %d are built)", N, SSM_ROWS * 32);
     WICK_REQUIRE(N <= 32 * SSM_ROWS, "ssm_mix: a state of %d numbers (up to %d are built)", N, 32 * SSM_ROWS);
     const int inner = H * P, channels = inner + 2 * G * N;
     WICK_REQUIRE(cols == 2 * inner + 2 * G * N + H, "ssm_mix: rows of %d numbers, %d expected", cols, 2 * inner + 2 * G * N + H);
