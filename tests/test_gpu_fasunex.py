@@ -231,6 +231,38 @@ def as_held(h, dtype):
 
 # ---------------------------------------------------------------------------
 # mechanisms alone
+def test_a_normed_sublayer_result_joins_the_stream_and_the_sum_is_normed_in_one_kernel():
+    """x <- x + rms(sum of the partial sums) * wb, then rms(x) * w in the activation type: widths that are and are not
+    multiples of four, every row or selected rows (one named twice), the sum's norm and the stream's norm with eps of
+    their own."""
+    g = torch.Generator().manual_seed(4)
+
+    def rms(v, eps):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+
+    for width, rows in ((40, 7), (101, 9), (258, 5), (2052, 33)):
+        x, d = 2 * torch.randn(rows, width, generator=g), torch.randn(3, rows, width, generator=g)
+        wb, w = 1 + 0.2 * torch.randn(width, generator=g), 1 + 0.3 * torch.randn(width, generator=g)
+        X = x.double() + rms(d.double().sum(0), 1e-5) * wb.double()
+        ref = rms(X, 3e-4) * w.double()
+        for dtype in DTYPES:
+            xd = x.to(DEV)
+            out = ops.stream_update(xd, d.to(DEV), rms=(wb.to(DEV), 1e-5), norm=("rms", w.to(DEV), 3e-4), out_dtype=TORCH[dtype])
+            tight(xd, X, "float32", f"the stream, width {width}")
+            tight(out, ref, dtype, f"its norm, width {width}")
+            xd = x.to(DEV)
+            idx = torch.tensor([rows - 1, 0, rows - 1], dtype=torch.int32)
+            out = ops.stream_update(xd, d.to(DEV), rms=(wb.to(DEV), 1e-5), norm=("rms", w.to(DEV), 3e-4), out_dtype=TORCH[dtype],
+                                    rows=idx.to(DEV))
+            tight(out, ref[idx.long()], dtype, f"selected rows, width {width}")
+            assert torch.equal(xd.cpu(), x)
+        # the norm alone, nothing added
+        xd = x.to(DEV)
+        out = ops.stream_update(xd, None, norm=("rms", w.to(DEV), 3e-4), out_dtype=torch.float32)
+        tight(out, rms(x.double(), 3e-4) * w.double(), "float32", f"the norm alone, width {width}")
+        assert torch.equal(xd.cpu(), x)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,d,scale", [(4, 2, 16, 0.3), (6, 1, 10, 0.33), (2, 2, 64, 0.125), (3, 3, 48, 0.2), (2, 1, 128, 0.09)])
 def test_attention_whose_keys_are_its_values(dtype, H, G, d, scale):

@@ -122,14 +122,16 @@ __global__ void to_activation_kernel(const float* __restrict__ x, T* __restrict_
 // One block per output row i; source row r = rows ? rows[i] : i.
 //   v = x[r] + f(sum of the partial sums, in index order), where f divides by the root mean square and multiplies
 //   by rms_w (if given), then multiplies by scale (if given);  v goes back to x[r] unless rows are selected (a row
-//   may be named twice, and nobody reads x afterwards then);  out[i] = tanh(alpha v) * w + b if w is given, else v.
-// With rms_w the sums wait in shared memory between the pass that squares them and the pass that uses them;
-// otherwise one pass does everything, four neighbours a thread where the width allows.
+//   may be named twice, and nobody reads x afterwards then);  out[i] = tanh(alpha v) * w + b if w and b are given,
+//   v / sqrt(mean(v^2) + out_eps) * w if w alone is given, else v.
+// With rms_w the sums wait in shared memory between the pass that squares them and the pass that uses them, and so does
+// v for the norm by its root mean square; otherwise one pass does everything, four neighbours a thread where the width
+// allows.
 template <typename TOut>
 __global__ void __launch_bounds__(1024)
 stream_update_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, int64_t split_stride,
                      const float* __restrict__ scale, const float* __restrict__ rms_w, float rms_eps,
-                     const float* __restrict__ alpha, const float* __restrict__ w, const float* __restrict__ b,
+                     const float* __restrict__ alpha, const float* __restrict__ w, const float* __restrict__ b, float out_eps,
                      const int* __restrict__ rows, TOut* __restrict__ out, int width) {
     extern __shared__ float smem[];
     float* row = smem;
@@ -144,7 +146,8 @@ stream_update_kernel(float* __restrict__ x, const float* __restrict__ delta, int
     float* xr = x + r * width;
     TOut* o = out ? out + (int64_t)i * width : nullptr;
     const bool vec = (width & 3) == 0 && (split_stride & 3) == 0;
-    float f = 1.f;
+    const bool out_rms = o && w && !b;                 // (the new row waits in shared memory for its mean square)
+    float f = 1.f, ss_out = 0.f;
     if (delta && rms_w) {
         float ss = 0.f;
         if (vec) {
@@ -184,7 +187,10 @@ stream_update_kernel(float* __restrict__ x, const float* __restrict__ delta, int
             float4 v;
             v.x = finish(j, xv.x, d.x); v.y = finish(j + 1, xv.y, d.y); v.z = finish(j + 2, xv.z, d.z); v.w = finish(j + 3, xv.w, d.w);
             if (delta && !rows) *reinterpret_cast<float4*>(xr + j) = v;
-            if (o) {
+            if (out_rms) {
+                *reinterpret_cast<float4*>(row + j) = v;
+                ss_out = fmaf(v.x, v.x, ss_out); ss_out = fmaf(v.y, v.y, ss_out); ss_out = fmaf(v.z, v.z, ss_out); ss_out = fmaf(v.w, v.w, ss_out);
+            } else if (o) {
                 if (w) {
                     st(o + j, tanhf(a * v.x) * w[j] + b[j]);
                     st(o + j + 1, tanhf(a * v.y) * w[j + 1] + b[j + 1]);
@@ -204,7 +210,24 @@ stream_update_kernel(float* __restrict__ x, const float* __restrict__ delta, int
             }
             const float v = finish(j, xr[j], d);
             if (delta && !rows) xr[j] = v;
-            if (o) st(o + j, w ? tanhf(a * v) * w[j] + b[j] : v);
+            if (out_rms) {
+                row[j] = v;
+                ss_out = fmaf(v, v, ss_out);
+            } else if (o) {
+                st(o + j, w ? tanhf(a * v) * w[j] + b[j] : v);
+            }
+        }
+    }
+    if (out_rms) {                                     // (a thread reads back the elements it wrote itself)
+        const float g = 1.0f / sqrtf(block_sum(ss_out, red) / (float)width + out_eps);
+        if (vec) {
+            for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(row + j);
+                st(o + j, (v.x * g) * w[j]); st(o + j + 1, (v.y * g) * w[j + 1]);
+                st(o + j + 2, (v.z * g) * w[j + 2]); st(o + j + 3, (v.w * g) * w[j + 3]);
+            }
+        } else {
+            for (int j = threadIdx.x; j < width; j += blockDim.x) st(o + j, (row[j] * g) * w[j]);
         }
     }
 }
@@ -285,10 +308,10 @@ __global__ void concat_activation_kernel(const float* __restrict__ a, const floa
 
 template <typename TOut>
 int stream_update(float* x, const float* delta, int splits, const float* scale, const float* rms_w, float rms_eps,
-                  const float* alpha, const float* w, const float* b, const int* rows, void* out, int n, int n_out, int width,
-                  cudaStream_t s) {
+                  const float* alpha, const float* w, const float* b, float out_eps, const int* rows, void* out, int n, int n_out,
+                  int width, cudaStream_t s) {
     WICK_REQUIRE(width > 0 && n >= 0 && n_out >= 0 && splits >= 0, "stream_update: bad sizes");
-    WICK_REQUIRE((w == nullptr) == (b == nullptr) && (w == nullptr) == (alpha == nullptr), "stream_update: the norm's three tensors come together");
+    WICK_REQUIRE((b == nullptr) == (alpha == nullptr) && (w || !b), "stream_update: a tanh norm has three tensors, a norm by the root mean square one");
     WICK_REQUIRE(!w || out, "stream_update: a norm needs a place for its result");
     WICK_REQUIRE(delta || (!scale && !rms_w), "stream_update: nothing to scale or to norm");
     if (n_out == 0) return 0;
@@ -301,7 +324,7 @@ int stream_update(float* x, const float* delta, int splits, const float* scale, 
     }
     const int threads = min(1024, max(64, ((width + 3) / 4 + 31) / 32 * 32));
     WICK_CUDA(launch(stream_update_kernel<TOut>, dim3(n_out), dim3(threads), smem, s, x, delta, splits, (int64_t)n * width, scale,
-                     rms_w, rms_eps, alpha, w, b, rows, (TOut*)out, width));
+                     rms_w, rms_eps, alpha, w, b, out_eps, rows, (TOut*)out, width));
     return check_launch("stream_update");
 }
 
@@ -341,16 +364,19 @@ WICK_API int wick_scaled_add_rmsnorm_f32(float* x, const float* delta, int split
 }
 
 // x: float32 [n, width]; delta: float32 [splits, n, width] or null; scale, rms_w: float32 [width] or null; alpha [1], w, b
-// [width]: the tanh norm's tensors or null; rows: int32 [n_out] or null (then n_out = n); out: [n_out, width] or null.
+// [width]: the tanh norm's tensors or null, or w alone with out_eps: a norm by the root mean square; rows: int32 [n_out] or
+// null (then n_out = n); out: [n_out, width] or null.
 WICK_API int wick_stream_update_bf16(float* x, const float* delta, int splits, const float* scale, const float* rms_w,
-                                     float rms_eps, const float* alpha, const float* w, const float* b, const int* rows,
-                                     void* out, int n, int n_out, int width, void* s) {
-    return stream_update<bf16>(x, delta, splits, scale, rms_w, rms_eps, alpha, w, b, rows, out, n, n_out, width, (cudaStream_t)s);
+                                     float rms_eps, const float* alpha, const float* w, const float* b, float out_eps,
+                                     const int* rows, void* out, int n, int n_out, int width, void* s) {
+    return stream_update<bf16>(x, delta, splits, scale, rms_w, rms_eps, alpha, w, b, out_eps, rows, out, n, n_out, width,
+                          (cudaStream_t)s);
 }
 WICK_API int wick_stream_update_f32(float* x, const float* delta, int splits, const float* scale, const float* rms_w,
-                                    float rms_eps, const float* alpha, const float* w, const float* b, const int* rows,
-                                    void* out, int n, int n_out, int width, void* s) {
-    return stream_update<float>(x, delta, splits, scale, rms_w, rms_eps, alpha, w, b, rows, out, n, n_out, width, (cudaStream_t)s);
+                                     float rms_eps, const float* alpha, const float* w, const float* b, float out_eps,
+                                     const int* rows, void* out, int n, int n_out, int width, void* s) {
+    return stream_update<float>(x, delta, splits, scale, rms_w, rms_eps, alpha, w, b, out_eps, rows, out, n, n_out, width,
+                          (cudaStream_t)s);
 }
 
 WICK_API int wick_gelu_gate_rows_bf16(const float* z, const void* table, const int* tokens, void* out, int64_t n, int dim,

@@ -593,8 +593,8 @@ def stream_update(x: torch.Tensor, delta: Optional[torch.Tensor], *, scale: Opti
     """The residual stream's own kernel.  ``x`` (float32 [n, width]) <- x + f(delta[0] + delta[1] + ...), in place:
     f divides the sum by its root mean square and multiplies it by a weight (``rms`` = (weight, eps)), then
     multiplies it by ``scale`` (float32 [width]), each where given.  With ``out_dtype`` the new rows also go out in
-    that type: after the norm ``("tanh", alpha, w, b)`` (tanh(alpha x) * w + b) if ``norm`` is given, else as they
-    are (for float32 that is ``x`` itself).  ``rows`` (int32 indices, a row may be named twice): only those rows go
+    that type: after the norm ``("tanh", alpha, w, b)`` (tanh(alpha x) * w + b) or ``("rms", w, eps)``
+    (x / sqrt(mean(x^2) + eps) * w) if ``norm`` is given, else as they are (for float32 that is ``x`` itself).  ``rows`` (int32 indices, a row may be named twice): only those rows go
     out, and ``x`` itself is left as it was."""
     _cuda("x", x, torch.float32)
     n, width = x.shape
@@ -610,12 +610,17 @@ def stream_update(x: torch.Tensor, delta: Optional[torch.Tensor], *, scale: Opti
     if rms_w is not None:
         _cuda("rms weight", rms_w, torch.float32, (width,))
     alpha = w = b = None
+    out_eps = 0.0
     if norm is not None:
-        _need(norm[0] == "tanh" and out_dtype is not None, "the stream kernel knows the tanh norm, and a norm has a result type")
-        _, alpha, w, b = norm
-        _cuda("alpha", alpha, torch.float32, (1,))
+        _need(norm[0] in ("tanh", "rms") and out_dtype is not None,
+              "the stream kernel knows the tanh norm and the norm by the root mean square, and a norm has a result type")
+        if norm[0] == "tanh":
+            _, alpha, w, b = norm
+            _cuda("alpha", alpha, torch.float32, (1,))
+            _cuda("b", b, torch.float32, (width,))
+        else:
+            _, w, out_eps = norm
         _cuda("w", w, torch.float32, (width,))
-        _cuda("b", b, torch.float32, (width,))
     if rows is not None:
         _cuda("rows", rows, torch.int32)
     n_out = n if rows is None else rows.numel()
@@ -625,8 +630,8 @@ def stream_update(x: torch.Tensor, delta: Optional[torch.Tensor], *, scale: Opti
     if delta is None and out is None:
         return x if out_dtype is not None else None
     name = f"wick_stream_update_{_dt(out)}" if out is not None else "wick_stream_update_f32"
-    _layer().call(name, "ppippfpppppiiip", _p(x), _p(delta), splits, _p(scale), _p(rms_w), float(rms_eps),
-                  _p(alpha), _p(w), _p(b), _p(rows), _p(out), n, n_out, width, _stream())
+    _layer().call(name, "ppippfpppfppiiip", _p(x), _p(delta), splits, _p(scale), _p(rms_w), float(rms_eps),
+                  _p(alpha), _p(w), _p(b), float(out_eps), _p(rows), _p(out), n, n_out, width, _stream())
     if out is not None:
         return out
     return x if out_dtype is not None else None

@@ -91,8 +91,9 @@ class RMSNorm(Norm):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, rows=rows)
 
     def add_forward(self, x, delta, out_dtype, rows=None, *, scale=None, rms=None):
-        if scale is not None or rms is not None:
-            return super().add_forward(x, delta, out_dtype, rows, scale=scale, rms=rms)
+        if scale is not None or rms is not None:              # (the stream's own kernel: the sum's factor or norm, then this norm)
+            return ops.stream_update(x, delta, scale=scale, rms=rms, norm=("rms", self.weight, self.eps),
+                                     out_dtype=out_dtype, rows=rows)
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, delta=delta, rows=rows)
 
     def scaled_add_forward(self, x, delta, alpha, out_dtype):
