@@ -78,7 +78,14 @@ CONFIG_FC = dict(architecture="Fasunex", vocab=300, width=128, norm={"eps": 1e-5
     layer(att(2, 1, 128, 0.09), moe(128, 4, 0, 2)),
     layer(att(4, 2, 64, 0.125), None),
 ])
-CONFIGS = {"FA": CONFIG_FA, "FB": CONFIG_FB, "FC": CONFIG_FC}
+# FD: a width that is no multiple of eight, heads of 40, 24, 8 and 6 numbers, five groups, seven taps, a chunk longer than the
+# prompts, a loop of three passes over one layer
+CONFIG_FD = dict(architecture="Fasunex", vocab=77, width=100, norm={"eps": 1e-6}, loop={"start": 1, "stop": 2, "times": 3}, layers=[
+    layer(att(3, 1, 40, 0.2), moe(36, 4, 1, 2)),
+    layer(par(left(5, 1, 24, 8, 0.2, mask=33, rot=(6, 1e4)), right(5, 12, 20, 5, 2, 1), 0.7, 1.3), moe(50, 7, 0, 3)),
+    layer(par(left(2, 2, 6, 6, 0.4, mask=300), right(1, 36, 9, 1, 7, 4), 1.0, 1.0), None),
+])
+CONFIGS = {"FA": CONFIG_FA, "FB": CONFIG_FB, "FC": CONFIG_FC, "FD": CONFIG_FD}
 _models = {}
 STD = 0.15
 
@@ -483,7 +490,7 @@ def test_mixers_side_by_side_add_up_with_their_factors(dtype):
 # ---------------------------------------------------------------------------
 # whole models through the engine
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["FA", "FB", "FC"])
+@pytest.mark.parametrize("name", ["FA", "FB", "FC", "FD"])
 def test_prompt_decoding_and_portions_agree_with_the_plain_model(name, dtype):
     cfg = CONFIGS[name]
     toks = random_tokens(cfg["vocab"], 230, seed=11)
@@ -534,7 +541,7 @@ def test_long_decoding_passes_chunk_edges_and_page_borders(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["FA", "FB"])
+@pytest.mark.parametrize("name", ["FA", "FB", "FD"])
 def test_a_batch_of_unequal_requests_equals_each_alone(name, dtype):
     cfg = CONFIGS[name]
     lens = [1, 65, 130, 9, 64]
