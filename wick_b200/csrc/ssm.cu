@@ -63,7 +63,9 @@ __device__ __forceinline__ float sum_parts(const float* __restrict__ parts, int 
 
 constexpr int SSM_CONV_TOKENS = 4;              // tokens a thread of the convolution takes (their loads are in flight together)
 
-// grid (ceil(tokens / SSM_CONV_TOKENS), ceil(channels / 256)).
+// grid (ceil(tokens / SSM_CONV_TOKENS), ceil(channels / 256)).  ONE: the projection came as a single set of sums (its loads
+// need no loop and go out together).
+template <bool ONE>
 __global__ void __launch_bounds__(256)
 ssm_conv_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int cols, int first_col, int channels, int taps,
                 const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state, int64_t record,
@@ -87,6 +89,7 @@ ssm_conv_kernel(const float* __restrict__ parts, int splits, int64_t split_strid
         rec[j] = state + (int64_t)slots[b] * record;
         acc[j] = b0;
     }
+#pragma unroll 4
     for (int k = 0; k < taps; ++k) {
         const float wk = w[(int64_t)c * taps + k];
         float u[SSM_CONV_TOKENS];
@@ -94,7 +97,8 @@ ssm_conv_kernel(const float* __restrict__ parts, int splits, int64_t split_strid
         for (int j = 0; j < SSM_CONV_TOKENS; ++j) {
             const int t = min(blockIdx.x * SSM_CONV_TOKENS + j, n - 1), sp = pos[j] - (taps - 1) + k;
             u[j] = 0.f;
-            if (sp >= first[j]) u[j] = sum_parts(parts, splits, split_stride, (int64_t)(t - (pos[j] - sp)) * cols + first_col + c);
+            const int64_t at = (int64_t)(t - (pos[j] - sp)) * cols + first_col + c;
+            if (sp >= first[j]) u[j] = ONE ? parts[at] : sum_parts(parts, splits, split_stride, at);
             else if (sp >= 0) u[j] = rec[j][(int64_t)(sp - (first[j] - (taps - 1))) * channels + c];
         }
 #pragma unroll
@@ -508,9 +512,14 @@ WICK_API int wick_ssm_mix(const float* parts, int splits, int n, int cols, int H
                  "ssm_mix: the chunked scan needs room for %d chunks", chunk > 0 ? n / chunk + n_seqs : 0);
     if (n == 0 || n_seqs == 0) return 0;
     const int64_t stride = (int64_t)n * cols;
-    WICK_CUDA(launch(ssm_conv_kernel, dim3(ceil_div(n, SSM_CONV_TOKENS), ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride,
-                     cols, inner, channels, taps, conv_w, conv_b, (const float*)state, record, slots, seq_of_token, positions, start,
-                     xbc, n));
+    const dim3 conv_grid(ceil_div(n, SSM_CONV_TOKENS), ceil_div(channels, 256));
+    if (splits == 1) {
+        WICK_CUDA(launch(ssm_conv_kernel<true>, conv_grid, dim3(256), 0, s, parts, splits, stride, cols, inner, channels, taps, conv_w,
+                         conv_b, (const float*)state, record, slots, seq_of_token, positions, start, xbc, n));
+    } else {
+        WICK_CUDA(launch(ssm_conv_kernel<false>, conv_grid, dim3(256), 0, s, parts, splits, stride, cols, inner, channels, taps, conv_w,
+                         conv_b, (const float*)state, record, slots, seq_of_token, positions, start, xbc, n));
+    }
     if (check_launch("ssm_conv")) return 1;
     if (taps > 1) {
         WICK_CUDA(launch(ssm_conv_state_kernel, dim3(n_seqs, ceil_div(channels, 256)), dim3(256), 0, s, parts, splits, stride, cols,
