@@ -1,7 +1,7 @@
 """wick_b200: a small model library with generation for one NVIDIA B200.
 
 Everything between a request's token ids and its next token for the Qwen3 dense
-decoder, the Nibotar decoder and the Tuguvik decoder: typed configuration and architecture registry, safetensors weights (or
+decoder and the Nibotar, Tuguvik, Fasunex and Sunosun decoders: typed configuration and architecture registry, safetensors weights (or
 seeded random ones), layers assembled from registered parts, a paged cache with
 a slot per sequence, one step function for batches of unequal sequences, a
 generation loop, sampling, and hand-written CUDA kernels for sm_100a.
@@ -17,10 +17,12 @@ from .config.nibotar import NibotarConfig
 from .config.qwen3 import Qwen3Config
 from .config.tuguvik import TuguvikConfig
 from .config.fasunex import FasunexConfig
+from .config.sunosun import SunosunConfig
 from .models import qwen3 as _qwen3  # registers the architecture  # noqa: F401
 from .models import nibotar as _nibotar  # noqa: F401
 from .models import tuguvik as _tuguvik  # noqa: F401
 from .models import fasunex as _fasunex  # noqa: F401
+from .models import sunosun as _sunosun  # noqa: F401
 from .models.model import Model
 from .models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .sampling.sampler import Rng, Sampler, SamplerConfig
@@ -41,6 +43,6 @@ def __getattr__(name):
 
 __all__ = ["Architecture", "ConfigError", "Engine", "FasunexConfig", "GenOptions", "GenResult", "LayerSpec", "Model", "ModelConfig",
            "ModelSpec", "NibotarConfig", "PartSpec", "Qwen3Config", "Rng", "SafeTensorsDir", "SafeTensorsError", "Sampler",
-           "SamplerConfig", "ScheduleEntry", "TuguvikConfig", "WeightError", "architecture_names", "config_from_json", "generate",
+           "SamplerConfig", "ScheduleEntry", "SunosunConfig", "TuguvikConfig", "WeightError", "architecture_names", "config_from_json", "generate",
            "get_architecture", "load_config", "load_weights", "register_architecture", "write_random_model",
            "write_safetensors"]

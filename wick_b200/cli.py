@@ -17,7 +17,7 @@ import time
 from typing import List, Optional
 
 USAGE = """\
-wick: run language models (Qwen3, Nibotar, Tuguvik, Fasunex) on one NVIDIA B200
+wick: run language models (Qwen3, Nibotar, Tuguvik, Fasunex, Sunosun) on one NVIDIA B200
 
 usage:
   wick run    <model-dir> --ids 1,2,3 [--ids 4,5 ...]   generate continuations of token-id prompts

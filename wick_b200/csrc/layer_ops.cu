@@ -267,6 +267,42 @@ __global__ void gate_rows_kernel(T* __restrict__ y, const float* __restrict__ pa
     st(y + i, ld(y + i) / (1.0f + expf(-g)));
 }
 
+// ---- an embedding with a factor and the positions' sinusoids ------------------------------------------------------
+// out[t][j] = table[token_t][j] * scale + s(p_t, j): s = sin(p f_i) for j = 2 i and cos(p f_i) for j = 2 i + 1, the angle the
+// float32 product of the position and the frequency f_i (float32 [ceil(width / 2)]); no sinusoid where `freq` is null.
+// One block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+embed_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ tokens, const int* __restrict__ positions,
+                      const float* __restrict__ freq, float scale, float* __restrict__ out, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T* row = table + (int64_t)tokens[t] * width;
+    const float p = (float)positions[t];
+    for (int i = threadIdx.x; 2 * i < width; i += blockDim.x) {
+        float sn = 0.f, cs = 0.f;
+        if (freq) sincosf(p * freq[i], &sn, &cs);
+        out[(int64_t)t * width + 2 * i] = fmaf(ld(row + 2 * i), scale, sn);
+        if (2 * i + 1 < width) out[(int64_t)t * width + 2 * i + 1] = fmaf(ld(row + 2 * i + 1), scale, cs);
+    }
+}
+
+// x[t][j] += (x0 ? x0[t][j] : 0) + (vec ? vec[j] : 0): what a pass over a range of layers begins with.
+__global__ void stream_offset_kernel(float* __restrict__ x, const float* __restrict__ x0, const float* __restrict__ vec, int64_t n,
+                                     int width) {
+    pdl_trigger();
+    pdl_wait();
+    x = fresh(x);
+    x0 = fresh(x0);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    if (x0) v += x0[i];
+    if (vec) v += vec[i % width];
+    x[i] = v;
+}
+
 // out = f_0 sum(a_0) + f_1 sum(a_1) + ...: up to four terms of partial sums (each added in index order), the terms
 // in the order given.
 struct SumTerms {
@@ -451,3 +487,23 @@ WICK_API int wick_weighted_sum(const float* a0, int s0, float f0, const float* a
     }
 WICK_CONCAT_ACTIVATION(wick_concat_activation_bf16, bf16)
 WICK_CONCAT_ACTIVATION(wick_concat_activation_f32, float)
+
+#define WICK_EMBED_SINUSOID(NAME, T)                                                                                         \
+    WICK_API int NAME(const void* table, const int* tokens, const int* positions, const float* freq, float scale, float* out, \
+                      int n, int width, void* s) {                                                                           \
+        WICK_REQUIRE(n >= 0 && width > 0, "embed_sinusoid: bad sizes");                                                      \
+        if (n == 0) return 0;                                                                                                \
+        WICK_CUDA(launch(embed_sinusoid_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)s, (const T*)table, tokens,          \
+                         positions, freq, scale, out, width));                                                               \
+        return check_launch("embed_sinusoid");                                                                               \
+    }
+WICK_EMBED_SINUSOID(wick_embed_sinusoid_bf16, bf16)
+WICK_EMBED_SINUSOID(wick_embed_sinusoid_f32, float)
+
+// x: float32 [n, width], changed in place; x0: float32 [n, width] or null; vec: float32 [width] or null.
+WICK_API int wick_stream_offset(float* x, const float* x0, const float* vec, int n, int width, void* s) {
+    const int64_t all = (int64_t)n * width;
+    if (all == 0) return 0;
+    WICK_CUDA(launch(stream_offset_kernel, dim3(ceil_div(all, 256)), dim3(256), 0, (cudaStream_t)s, x, x0, vec, all, width));
+    return check_launch("stream_offset");
+}

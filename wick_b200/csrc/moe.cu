@@ -31,11 +31,12 @@ template <typename T> __device__ __forceinline__ float dot_row(const T* __restri
 
 constexpr int ROWS_PER_WARP = 4;
 
-// grid (n * top, ceil(ff / (warps * ROWS_PER_WARP))).  gate_up: [experts][2][ff][width] (gate rows, then up rows).
+// grid (n * top, ceil(ff / (warps * ROWS_PER_WARP))).  gate_up: [experts][2][ff][width] (gate rows, then up rows); not `gated`:
+// [experts][ff][width] and hidden = max(up x, 0)^2.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ table, int top, int n_experts,
-              const T* __restrict__ gate_up, T* __restrict__ hidden, int width, int ff) {
+              const T* __restrict__ gate_up, T* __restrict__ hidden, int width, int ff, int gated) {
     extern __shared__ float xs[];
     pdl_trigger();
     pdl_wait();
@@ -46,13 +47,17 @@ moe_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens, const int
     __syncthreads();
     const int ex = table[(int64_t)tokens[t] * top + c];
     if (ex < 0 || ex >= n_experts) return;                                   // (a table that names no expert adds nothing)
-    const T* wg = gate_up + (int64_t)ex * 2 * ff * width;
+    const T* wg = gate_up + (int64_t)ex * (gated ? 2 : 1) * ff * width;
     const T* wu = wg + (int64_t)ff * width;
     const int f0 = (blockIdx.y * (blockDim.x >> 5) + warp) * ROWS_PER_WARP;
     for (int f = f0; f < min(f0 + ROWS_PER_WARP, ff); ++f) {
         const float g = dot_row(wg + (int64_t)f * width, xs, width, lane);
-        const float u = dot_row(wu + (int64_t)f * width, xs, width, lane);
-        if (lane == 0) st(hidden + ((int64_t)t * top + c) * ff + f, g / (1.0f + expf(-g)) * u);
+        if (gated) {
+            const float u = dot_row(wu + (int64_t)f * width, xs, width, lane);
+            if (lane == 0) st(hidden + ((int64_t)t * top + c) * ff + f, g / (1.0f + expf(-g)) * u);
+        } else if (lane == 0) {
+            st(hidden + ((int64_t)t * top + c) * ff + f, fmaxf(g, 0.f) * fmaxf(g, 0.f));
+        }
     }
 }
 
@@ -93,15 +98,17 @@ moe_down_kernel(const T* __restrict__ hidden, const int* __restrict__ tokens, co
 // then its warps take matrix rows, four each (for the gated pair: four gate rows and four up rows),
 // and multiply them with the inputs of two pairs at a time, 16 bytes a lane and trip, float32 sums
 // (a lane's elements in index order, the 32 lanes by the butterfly).
-//   GATED: in = x [n, k], w = [experts][2][rows][k], hidden[pair][row] = silu(g) * u
-//   else : in = hidden [n * top, k], w = [experts][rows][k], y[pair][row] = the product (float32)
-template <typename T, bool GATED>
+//   MODE 1: in = x [n, k], w = [experts][2][rows][k], hidden[pair][row] = silu(g) * u
+//   MODE 2: in = x [n, k], w = [experts][rows][k], hidden[pair][row] = max(g, 0)^2
+//   MODE 0: in = hidden [n * top, k], w = [experts][rows][k], y[pair][row] = the product (float32)
+template <typename T, int MODE>
 __global__ void __launch_bounds__(128)
 moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens, const int* __restrict__ table, int top,
                        int n_pairs, const T* __restrict__ w, T* __restrict__ hidden_out, float* __restrict__ y_out, int rows,
                        int k) {
     extern __shared__ int list[];
     __shared__ int count;
+    constexpr bool GATED = MODE == 1, FROM_X = MODE != 0;
     pdl_trigger();
     pdl_wait();
     in = fresh(in);
@@ -127,7 +134,7 @@ moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens,
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 const int p = list[min(m0 + u, n_list - 1)];
-                xin[u] = in + (int64_t)(GATED ? p / top : p) * k;
+                xin[u] = in + (int64_t)(FROM_X ? p / top : p) * k;
 #pragma unroll
                 for (int r = 0; r < ROWS_PER_WARP; ++r) ag[r][u] = au[r][u] = 0.f;
             }
@@ -158,6 +165,7 @@ moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens,
                     if (lane == 0 && m0 + u < n_list) {
                         const int p = list[m0 + u];
                         if (GATED) st(hidden_out + (int64_t)p * rows + r0 + r, gs / (1.0f + expf(-gs)) * us);
+                        else if (MODE == 2) st(hidden_out + (int64_t)p * rows + r0 + r, fmaxf(gs, 0.f) * fmaxf(gs, 0.f));
                         else y_out[(int64_t)p * rows + r0 + r] = gs;
                     }
                 }
@@ -173,7 +181,7 @@ moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens,
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int p = list[min(m0 + u, n_list - 1)];
-                xin[u] = in + (int64_t)(GATED ? p / top : p) * k;
+                xin[u] = in + (int64_t)(FROM_X ? p / top : p) * k;
             }
             for (int j = lane; j < k; j += 32) {
                 const float g = ld(wg + j), up = GATED ? ld(wu + j) : 0.f;
@@ -190,6 +198,7 @@ moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens,
                 if (lane == 0 && m0 + u < n_list) {
                     const int p = list[m0 + u];
                     if (GATED) st(hidden_out + (int64_t)p * rows + r, g / (1.0f + expf(-g)) * up);
+                    else if (MODE == 2) st(hidden_out + (int64_t)p * rows + r, fmaxf(g, 0.f) * fmaxf(g, 0.f));
                     else y_out[(int64_t)p * rows + r] = g;
                 }
             }
@@ -318,16 +327,35 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 
 // ---- experts chosen by a router ---------------------------------------------------------------
 // One warp per token.  z = the router's logits (float32 partial sums, added in index order) over all its outputs;
-// s = softmax(z); the `top` outputs with the largest s + correction are chosen (the lowest index among equals),
-// one after the other; choice[t][c] = the output's index, weight[t][c] = s of it (divided by the chosen ones' sum
-// if `renormalize`).  Outputs from n_experts on stand for experts without matrices; the kernels that walk the
-// experts' matrices pass them over.  ident[t] = t: with it as "token ids", choice is the table those kernels read.
+// s = softmax(z) over the outputs (`scoring` 0) or sigmoid(z) of each (`scoring` 1); the choice score of an output is
+// s + correction.  With `groups` > 0 the outputs form that many equal groups of neighbours; a group's score is the sum of
+// its two largest choice scores (of its only one, in groups of one); only outputs of the `keep` best groups can be chosen
+// (the others' choice scores count as minus infinity).  The `top` outputs with the largest choice scores are chosen (the
+// lowest index among equals), one after the other; choice[t][c] = the output's index, weight[t][c] = s of it, divided by
+// (the chosen ones' sum + norm_eps) if `renormalize`, times `scale`.  Outputs from n_experts on stand for experts without
+// matrices; the kernels that walk the experts' matrices pass them over.  ident[t] = t: with it as "token ids", choice is
+// the table those kernels read.
+__device__ __forceinline__ void warp_best(float& best, int& at) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) {
+            best = ob;
+            at = oa;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(32)
 moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int n_out, const float* __restrict__ correction,
-                  int top, int renormalize, int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ ident) {
+                  int top, int renormalize, int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ ident,
+                  int scoring, int groups, int keep, float scale, float norm_eps) {
     extern __shared__ float sm[];
     float* score = sm;                                                  // [n_out]
     float* pick = sm + n_out;                                           // [n_out]: score + correction, -inf once chosen
+    float* gscore = pick + n_out;                                       // [groups]: -inf once kept
+    float* gkept = gscore + groups;                                     // [groups]: 1 if kept
     pdl_trigger();
     pdl_wait();
     parts = fresh(parts);
@@ -339,20 +367,59 @@ moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_str
         score[e] = z;
         m = fmaxf(m, z);
     }
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < n_out; e += 32) {
-        const float p = expf(score[e] - m);
-        score[e] = p;
-        sum += p;
+    if (scoring == 0) {
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < n_out; e += 32) {
+            const float p = expf(score[e] - m);
+            score[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < n_out; e += 32) score[e] *= inv;
+    } else {
+        for (int e = lane; e < n_out; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
     }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < n_out; e += 32) {
-        score[e] *= inv;
-        pick[e] = score[e] + (correction ? correction[e] : 0.f);
-    }
+    for (int e = lane; e < n_out; e += 32) pick[e] = score[e] + (correction ? correction[e] : 0.f);
     __syncwarp();
+    if (groups > 0) {
+        const int per = n_out / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;                         // the two largest of the group
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = pick[e];
+                if (v > a) {
+                    b = a;
+                    a = v;
+                } else if (v > b) {
+                    b = v;
+                }
+            }
+            gscore[g] = per > 1 ? a + b : a;
+            gkept[g] = 0.f;
+        }
+        __syncwarp();
+        for (int c = 0; c < keep; ++c) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32)
+                if (gscore[g] > best) {
+                    best = gscore[g];
+                    at = g;
+                }
+            warp_best(best, at);
+            if (at >= groups) break;
+            if (lane == 0) {
+                gscore[at] = -INFINITY;
+                gkept[at] = 1.f;
+            }
+            __syncwarp();
+        }
+        for (int e = lane; e < n_out; e += 32)
+            if (gkept[e / per] == 0.f) pick[e] = -INFINITY;
+        __syncwarp();
+    }
     float chosen_sum = 0.f;
     for (int c = 0; c < top; ++c) {
         float best = -INFINITY;
@@ -362,15 +429,7 @@ moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_str
                 best = pick[e];
                 at = e;
             }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ob > best || (ob == best && oa < at)) {
-                best = ob;
-                at = oa;
-            }
-        }
+        warp_best(best, at);
         if (at >= n_out) at = 0;                                        // (nothing left to choose: scores that are no numbers)
         if (lane == 0) {
             choice[(int64_t)t * top + c] = at;
@@ -380,8 +439,12 @@ moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_str
         chosen_sum += score[at];
         __syncwarp();
     }
-    if (renormalize && lane == 0)
-        for (int c = 0; c < top; ++c) weight[(int64_t)t * top + c] /= chosen_sum;
+    if (lane == 0)
+        for (int c = 0; c < top; ++c) {
+            float w = weight[(int64_t)t * top + c];
+            if (renormalize) w /= (chosen_sum + norm_eps);
+            weight[(int64_t)t * top + c] = w * scale;
+        }
     if (lane == 0 && ident) ident[t] = t;
 }
 
@@ -413,7 +476,8 @@ moe_down_pair_kernel(const T* __restrict__ hidden, const int* __restrict__ token
 template <typename T>
 __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ row_of, const int* __restrict__ choice,
                                             const float* __restrict__ weight, const T* __restrict__ x, int n_experts, int top,
-                                            float* __restrict__ out, int width) {
+                                            float* __restrict__ out, int width, const float* __restrict__ base, int base_splits,
+                                            int64_t base_stride, const float* __restrict__ gate, int gate_splits, int64_t gate_stride) {
     pdl_trigger();
     pdl_wait();
     y = fresh(y);
@@ -421,7 +485,15 @@ __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const i
     choice = fresh(choice);
     weight = fresh(weight);
     x = fresh(x);
+    base = fresh(base);
+    gate = fresh(gate);
     const int t = blockIdx.x;
+    float bf = 1.f;                                                     // the factor of what every token uses: sigmoid of the gate's number
+    if (base && gate) {
+        float g = 0.f;
+        for (int s = 0; s < gate_splits; ++s) g += gate[s * gate_stride + t];
+        bf = 1.0f / (1.0f + expf(-g));
+    }
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         float sum = 0.f;
         for (int c = 0; c < top; ++c) {
@@ -434,25 +506,36 @@ __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const i
                 sum = fmaf(wgt, ld(x + (int64_t)t * width + j), sum);
             }
         }
+        if (base) {
+            float v = 0.f;
+            for (int s = 0; s < base_splits; ++s) v += base[s * base_stride + (int64_t)t * width + j];
+            sum = fmaf(bf, v, sum);
+        }
         out[(int64_t)t * width + j] = sum;
     }
 }
 
 template <typename T>
 int moe_up(const void* x, const int* tokens, const int* table, int top, int n_experts, const void* gate_up, void* hidden, int n,
-           int width, int ff, cudaStream_t s) {
+           int width, int ff, int gated, cudaStream_t s) {
     WICK_REQUIRE(top > 0 && n_experts > 0 && width > 0 && ff > 0, "moe_up: bad sizes");
     if (n == 0) return 0;
     const int warps = 4;
     if ((int64_t)n * top <= PAIRS_BY_EXPERT) {
-        WICK_CUDA(launch(moe_expert_rows_kernel<T, true>, dim3(n_experts, ceil_div(ff, warps * ROWS_PER_WARP)), dim3(warps * 32),
-                         (size_t)n * top * sizeof(int), s, (const T*)x, tokens, table, top, n * top, (const T*)gate_up, (T*)hidden,
-                         (float*)nullptr, ff, width));
+        if (gated) {
+            WICK_CUDA(launch(moe_expert_rows_kernel<T, 1>, dim3(n_experts, ceil_div(ff, warps * ROWS_PER_WARP)), dim3(warps * 32),
+                             (size_t)n * top * sizeof(int), s, (const T*)x, tokens, table, top, n * top, (const T*)gate_up, (T*)hidden,
+                             (float*)nullptr, ff, width));
+        } else {
+            WICK_CUDA(launch(moe_expert_rows_kernel<T, 2>, dim3(n_experts, ceil_div(ff, warps * ROWS_PER_WARP)), dim3(warps * 32),
+                             (size_t)n * top * sizeof(int), s, (const T*)x, tokens, table, top, n * top, (const T*)gate_up, (T*)hidden,
+                             (float*)nullptr, ff, width));
+        }
         return check_launch("moe_up");
     }
     WICK_REQUIRE((size_t)width * 4 <= 48 * 1024, "moe_up: width %d is beyond %d", width, 48 * 1024 / 4);
     WICK_CUDA(launch(moe_up_kernel<T>, dim3(n * top, ceil_div(ff, warps * ROWS_PER_WARP)), dim3(warps * 32), (size_t)width * 4, s,
-                     (const T*)x, tokens, table, top, n_experts, (const T*)gate_up, (T*)hidden, width, ff));
+                     (const T*)x, tokens, table, top, n_experts, (const T*)gate_up, (T*)hidden, width, ff, gated));
     return check_launch("moe_up");
 }
 
@@ -464,7 +547,7 @@ int moe_down(const void* hidden, const int* tokens, const int* table, int top, i
     const int warps = 4;
     if (y && (int64_t)n * top <= PAIRS_BY_EXPERT) {
         // y [n * top, width] (float32, zero on entry): every pair's product, then the sum per token
-        WICK_CUDA(launch(moe_expert_rows_kernel<T, false>, dim3(n_experts, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32),
+        WICK_CUDA(launch(moe_expert_rows_kernel<T, 0>, dim3(n_experts, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32),
                          (size_t)n * top * sizeof(int), s, (const T*)hidden, tokens, table, top, n * top, (const T*)down, (T*)nullptr,
                          y, width, ff));
         WICK_CUDA(launch(moe_combine_kernel, dim3(n), dim3(256), 0, s, (const float*)y, (const int*)nullptr, top, weight, base,
@@ -485,12 +568,12 @@ using namespace wick;
 typedef __nv_bfloat16 bf16;
 
 WICK_API int wick_moe_up_bf16(const void* x, const int* tokens, const int* table, int top, int n_experts, const void* gate_up,
-                              void* hidden, int n, int width, int ff, void* s) {
-    return moe_up<bf16>(x, tokens, table, top, n_experts, gate_up, hidden, n, width, ff, (cudaStream_t)s);
+                              void* hidden, int n, int width, int ff, int gated, void* s) {
+    return moe_up<bf16>(x, tokens, table, top, n_experts, gate_up, hidden, n, width, ff, gated, (cudaStream_t)s);
 }
 WICK_API int wick_moe_up_f32(const void* x, const int* tokens, const int* table, int top, int n_experts, const void* gate_up,
-                             void* hidden, int n, int width, int ff, void* s) {
-    return moe_up<float>(x, tokens, table, top, n_experts, gate_up, hidden, n, width, ff, (cudaStream_t)s);
+                             void* hidden, int n, int width, int ff, int gated, void* s) {
+    return moe_up<float>(x, tokens, table, top, n_experts, gate_up, hidden, n, width, ff, gated, (cudaStream_t)s);
 }
 WICK_API int wick_moe_down_bf16(const void* hidden, const int* tokens, const int* table, int top, int n_experts, const void* down,
                                 float weight, const float* base, int base_splits, float* y, float* out, int n, int width, int ff,
@@ -542,12 +625,17 @@ WICK_API int wick_moe_combine(const float* y, const int* row_of, int top, float 
 // parts: float32 [splits, n, n_out] (the router's logits as partial sums); correction: float32 [n_out] or null;
 // choice: int32 [n, top]; weight: float32 [n, top]; ident: int32 [n] or null.
 WICK_API int wick_moe_router(const float* parts, int splits, int n, int n_out, const float* correction, int top, int renormalize,
-                             int* choice, float* weight, int* ident, void* s) {
+                             int* choice, float* weight, int* ident, int scoring, int groups, int keep, float scale, float norm_eps,
+                             void* s) {
     WICK_REQUIRE(splits >= 1 && n_out > 0 && top > 0 && top <= n_out, "moe_router: bad sizes");
-    WICK_REQUIRE((size_t)n_out * 8 <= 48 * 1024, "moe_router: %d outputs are beyond one block's shared memory", n_out);
+    WICK_REQUIRE(scoring == 0 || scoring == 1, "moe_router: scores are a softmax (0) or sigmoids (1)");
+    WICK_REQUIRE(groups == 0 || (groups > 0 && n_out % groups == 0 && keep > 0 && keep <= groups && keep * (n_out / groups) >= top),
+                 "moe_router: %d outputs do not form %d equal groups of which %d hold %d choices", n_out, groups, keep, top);
+    WICK_REQUIRE((size_t)(n_out + groups) * 8 <= 48 * 1024, "moe_router: %d outputs are beyond one block's shared memory", n_out);
     if (n == 0) return 0;
-    WICK_CUDA(launch(moe_router_kernel, dim3(n), dim3(32), (size_t)n_out * 2 * sizeof(float), (cudaStream_t)s, parts, splits,
-                     (int64_t)n * n_out, n_out, correction, top, renormalize, choice, weight, ident));
+    WICK_CUDA(launch(moe_router_kernel, dim3(n), dim3(32), (size_t)(n_out + groups) * 2 * sizeof(float), (cudaStream_t)s, parts, splits,
+                     (int64_t)n * n_out, n_out, correction, top, renormalize, choice, weight, ident, scoring, groups, keep, scale,
+                     norm_eps));
     return check_launch("moe_router");
 }
 
@@ -559,7 +647,7 @@ static int moe_expert_down(const void* hidden, const int* tokens, const int* tab
     if (n == 0) return 0;
     const int warps = 4;
     if ((int64_t)n * top <= PAIRS_BY_EXPERT) {
-        WICK_CUDA(launch(moe_expert_rows_kernel<T, false>, dim3(n_experts, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32),
+        WICK_CUDA(launch(moe_expert_rows_kernel<T, 0>, dim3(n_experts, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32),
                          (size_t)n * top * sizeof(int), s, (const T*)hidden, tokens, table, top, n * top, (const T*)down, (T*)nullptr,
                          y, width, ff));
         return check_launch("moe_expert_down");
@@ -580,12 +668,16 @@ WICK_API int wick_moe_expert_down_f32(const void* hidden, const int* tokens, con
 
 // y: float32 rows; row_of: int32 [n, top] or null (rows in pair order); choice: int32 [n, top]; weight: float32 [n, top];
 // x: [n, width] or null (what an expert without matrices returns); out: float32 [n, width].
+// base: float32 [base_splits, n, width] or null: what every token uses, added with the factor sigmoid(sum of gate[:, t]) where
+// gate (float32 [gate_splits, n]) is given, else 1.
 #define WICK_MOE_COMBINE_WEIGHTED(NAME, T)                                                                                    \
     WICK_API int NAME(const float* y, const int* row_of, const int* choice, const float* weight, const void* x, int n_experts, \
-                      int top, float* out, int n, int width, void* s) {                                                       \
+                      int top, float* out, int n, int width, const float* base, int base_splits, const float* gate,           \
+                      int gate_splits, void* s) {                                                                             \
         if (n == 0) return 0;                                                                                                 \
         WICK_CUDA(launch(moe_combine_weighted_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)s, y, row_of, choice, weight,     \
-                         (const T*)x, n_experts, top, out, width));                                                            \
+                         (const T*)x, n_experts, top, out, width, base, base_splits, (int64_t)n * width, gate, gate_splits,    \
+                         (int64_t)n));                                                                                         \
         return check_launch("moe_combine_weighted");                                                                          \
     }
 WICK_MOE_COMBINE_WEIGHTED(wick_moe_combine_weighted_bf16, bf16)

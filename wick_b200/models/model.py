@@ -137,12 +137,15 @@ class Model:
         (float32 [tokens, width], everything added)."""
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
-        h = Hidden(self.embedding.forward(batch.tokens))
+        if getattr(self.embedding, "NEEDS_POSITIONS", False):
+            h = Hidden(self.embedding.forward(batch.tokens, batch.positions))
+        else:
+            h = Hidden(self.embedding.forward(batch.tokens))
         if any(getattr(p, "NEEDS_EMBEDDING_OUTPUT", False) for p in self.shared.values()):
             batch.memo["embedding_output"] = h.x.clone()         # (the stream itself is changed in place by the layers)
         for i, e in enumerate(self.spec.schedule):
             if e.before is not None:
-                self.shared[e.before].forward(h, batch)
+                self.shared[e.before].forward(h, batch, e.before_index)
             src = i if e.read_cache_of is None else e.read_cache_of
             h = self.blocks[e.layer].forward(h, batch, cache.view(src, batch), e.read_cache_of is None)
             if tap is not None:

@@ -64,11 +64,13 @@ class ScheduleEntry:
     """Run ``layer``.  ``read_cache_of`` is the index (in the schedule) of an
     earlier entry whose cache this entry's mixer reads without writing.  ``before`` names
     the place of a shared part of the category ``side`` that changes the stream right before
-    the layer runs (what a pass over a range of layers begins with)."""
+    the layer runs (what a pass over a range of layers begins with); ``before_index`` is the number
+    that part is given (the number of the pass)."""
 
     layer: int
     read_cache_of: Optional[int] = None
     before: Optional[str] = None
+    before_index: int = 0
 
 
 @dataclasses.dataclass(frozen=True)

@@ -522,7 +522,7 @@ def attention_decode_parts_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, hea
 # Mechanisms of layers beyond the plain pre-norm decoder: the norm after the residual sum, a
 # feed-forward's squared ReLU, the soft cap of logits, attention with options (csrc/attn_masked.cu)
 # and experts chosen by a table (csrc/moe.cu).
-LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "attn_multi.cu", "moe.cu", "ssm.cu"]
+LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "attn_multi.cu", "moe.cu", "ssm.cu", "gla.cu"]
 
 MASKS = {"causal": 0, "block": 1, "window": 2}
 PAIRINGS = {"neighbours": 0, "halves": 1}
@@ -1044,17 +1044,19 @@ def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, 
 
 def moe_table_up(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     """hidden[t, c] = silu(gate x_t) * (up x_t) with the matrices of expert ``table[tokens[t], c]``.
-    x [n, width]; table int32 [vocab, top]; gate_up [experts, 2, ff, width] -> [n, top, ff]."""
+    x [n, width]; table int32 [vocab, top]; gate_up [experts, 2, ff, width] -> [n, top, ff].  With ``gate_up`` of shape
+    [experts, 1, ff, width] the experts have one matrix and hidden = max(up x_t, 0)^2."""
     _cuda("x", x)
     n, width = x.shape
     _cuda("tokens", tokens, torch.int32, (n,))
     _cuda("table", table, torch.int32)
     _cuda("gate_up", gate_up, x.dtype)
-    _need(gate_up.dim() == 4 and gate_up.shape[1] == 2 and gate_up.shape[3] == width, "gate_up must be [experts, 2, ff, width]")
+    _need(gate_up.dim() == 4 and gate_up.shape[1] in (1, 2) and gate_up.shape[3] == width,
+          "gate_up must be [experts, 2 or 1, ff, width]")
     top, ff = table.shape[1], gate_up.shape[2]
     hidden = torch.empty((n, top, ff), dtype=x.dtype, device=x.device)
-    _layer().call(f"wick_moe_up_{_dt(x)}", "pppiippiiip", _p(x), _p(tokens), _p(table), top, gate_up.shape[0], _p(gate_up),
-                  _p(hidden), n, width, ff, _stream())
+    _layer().call(f"wick_moe_up_{_dt(x)}", "pppiippiiiip", _p(x), _p(tokens), _p(table), top, gate_up.shape[0], _p(gate_up),
+                  _p(hidden), n, width, ff, 1 if gate_up.shape[1] == 2 else 0, _stream())
     return hidden
 
 
@@ -1131,23 +1133,31 @@ def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weight: float, base: Opti
 
 
 # ---- experts chosen by a router ---------------------------------------------------------------------------------------
-def moe_router(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, *, renormalize: bool = False
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_router(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, *, renormalize: bool = False,
+               scores: str = "softmax", groups: int = 0, keep: int = 0, scale: float = 1.0, norm_eps: float = 0.0
                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """From the router's logits (float32 partial sums [splits, n, outputs]): scores = softmax over the outputs; the ``top``
-    outputs with the largest score + ``correction`` (float32 [outputs] or None) are chosen, the lowest index among equals.
-    Returns (choice int32 [n, top], weight float32 [n, top]: the chosen outputs' scores, divided by their sum if
-    ``renormalize``; ident int32 [n] = 0 .. n - 1: with it as token ids, ``choice`` is the table of the kernels that
-    read experts from a table)."""
+    """From the router's logits (float32 partial sums [splits, n, outputs]): scores = softmax over the outputs, or the
+    sigmoid of each (``scores``); the ``top`` outputs with the largest score + ``correction`` (float32 [outputs] or None)
+    are chosen, the lowest index among equals.  ``groups`` > 0: the outputs form that many equal groups of neighbours, a
+    group's score is the sum of its two largest corrected scores, and only outputs of the ``keep`` best groups can be chosen.
+    Returns (choice int32 [n, top], weight float32 [n, top]: the chosen outputs' scores, divided by (their sum +
+    ``norm_eps``) if ``renormalize``, times ``scale``; ident int32 [n] = 0 .. n - 1: with it as token ids, ``choice`` is the
+    table of the kernels that read experts from a table)."""
     _cuda("logits", logits, torch.float32)
     _need(logits.dim() == 3, "the router's logits come as partial sums [splits, n, outputs]")
+    _need(scores in ROUTER_SCORES, f"router scores are {', '.join(ROUTER_SCORES)}, not {scores!r}")
     splits, n, n_out = logits.shape
     if correction is not None:
         _cuda("correction", correction, torch.float32, (n_out,))
     choice = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     ident = torch.empty((n,), dtype=torch.int32, device=logits.device)
-    _layer().call("wick_moe_router", "piiipiipppp", _p(logits), splits, n, n_out, _p(correction), int(top), 1 if renormalize else 0,
-                  _p(choice), _p(weight), _p(ident), _stream())
+    _layer().call("wick_moe_router", "piiipiipppiiiffp", _p(logits), splits, n, n_out, _p(correction), int(top), 1 if renormalize else 0,
+                  _p(choice), _p(weight), _p(ident), ROUTER_SCORES[scores], int(groups), int(keep), float(scale), float(norm_eps),
+                  _stream())
     return choice, weight, ident
 
 
@@ -1169,10 +1179,13 @@ def moe_expert_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Ten
 
 
 def moe_combine_weighted(y: torch.Tensor, row_of: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
-                         x: Optional[torch.Tensor], n_experts: int) -> torch.Tensor:
+                         x: Optional[torch.Tensor], n_experts: int, base: Optional[torch.Tensor] = None,
+                         base_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """float32 out[t] = sum over c of weight[t, c] * r(t, c): r is row ``row_of[t, c]`` of ``y`` (row t * top + c without
     ``row_of``) where ``choice[t, c]`` < ``n_experts``, and ``x[t]`` itself where it is ``n_experts`` or more (an expert
-    that returns its input; nothing if ``x`` is None).  y float32 [rows, width]; x [n, width]."""
+    that returns its input; nothing if ``x`` is None).  y float32 [rows, width]; x [n, width].  ``base`` (float32 partial
+    sums [splits, n, width]): what every token uses, added to the sum, times sigmoid(g_t) where ``base_gate`` (float32
+    partial sums [splits, n, 1]) gives a number g_t per token."""
     _cuda("y", y, torch.float32)
     _cuda("choice", choice, torch.int32)
     n, top = choice.shape
@@ -1184,10 +1197,103 @@ def moe_combine_weighted(y: torch.Tensor, row_of: Optional[torch.Tensor], choice
     if x is not None:
         _cuda("x", x, None, (n, width))
         dt = _dt(x)
+    bs = gs = 0
+    if base is not None:
+        _cuda("base", base, torch.float32)
+        _need(base.dim() == 3 and tuple(base.shape[1:]) == (n, width), f"base must be [splits, {n}, {width}]")
+        bs = base.shape[0]
+    if base_gate is not None:
+        _cuda("base_gate", base_gate, torch.float32)
+        _need(base is not None and base_gate.dim() == 3 and tuple(base_gate.shape[1:]) == (n, 1), f"base_gate must be [splits, {n}, 1]")
+        gs = base_gate.shape[0]
     out = torch.empty((n, width), dtype=torch.float32, device=y.device)
-    _layer().call(f"wick_moe_combine_weighted_{dt}", "pppppiipiip", _p(y), _p(row_of), _p(choice), _p(weight), _p(x), int(n_experts),
-                  top, _p(out), n, width, _stream())
+    _layer().call(f"wick_moe_combine_weighted_{dt}", "pppppiipiipipip", _p(y), _p(row_of), _p(choice), _p(weight), _p(x), int(n_experts),
+                  top, _p(out), n, width, _p(base), bs, _p(base_gate), gs, _stream())
     return out
+
+
+# ---- gated linear attention -------------------------------------------------------------------------------------------
+GLA_CHUNK = 64            # tokens of one chunk of a long prompt's scan
+GLA_CHUNKED_FROM = 192    # a prompt step of this many tokens or more is scanned in chunks
+
+
+def gla_mix(parts: torch.Tensor, *, heads: int, key_dim: int, v_dim: int, w2: torch.Tensor, b2: Optional[torch.Tensor], q_scale: float,
+            tau: float, records: torch.Tensor, batch) -> torch.Tensor:
+    """The recurrence of a step's tokens.  ``parts``: the input projection's float32 partial sums [splits, n, cols], a row
+    laid out [q: H dk | k: H dk | v: H dv | g: H dv | low: r].  q <- q * ``q_scale``; the decay per key channel is
+    a = sigmoid(w2 low + b2)^(1 / tau) (``w2`` float32 [H dk, r]); per head S <- diag(a) S + k v^T and o = S^T q.
+    ``records``: float32 [slots, H dv dk], a sequence's state (a column of S lies together), read and brought up to date for
+    the slots of ``batch``.  Returns o float32 [n, H dv]."""
+    _cuda("parts", parts, torch.float32)
+    _need(parts.dim() == 3, "the projection comes as partial sums [splits, n, cols]")
+    splits, n, cols = parts.shape
+    hk, hv = heads * key_dim, heads * v_dim
+    _cuda("w2", w2, torch.float32)
+    _need(w2.dim() == 2 and w2.shape[0] == hk, f"w2 must be [{hk}, rank], is {tuple(w2.shape)}")
+    rank = w2.shape[1]
+    if b2 is not None:
+        _cuda("b2", b2, torch.float32, (hk,))
+    _cuda("records", records, torch.float32)
+    _need(records.dim() == 2 and records.shape[1] == hv * key_dim, f"records must be [slots, {hv * key_dim}], are {tuple(records.shape)}")
+    _need(n == batch.n_tokens, f"{n} rows, the batch has {batch.n_tokens} tokens")
+    qkav = torch.empty((n, 3 * hk + hv), dtype=torch.float32, device=parts.device)
+    y = torch.empty((n, hv), dtype=torch.float32, device=parts.device)
+    max_q = 1 if batch.is_decode else 0          # (0: unknown to the host, as in a captured prompt step)
+    chunk, chunks, chunk_state, chunk_decay = GLA_CHUNK, 0, None, None
+    if not batch.is_decode and n >= GLA_CHUNKED_FROM:
+        chunks = n // chunk + batch.n_seqs
+        chunk_state = torch.empty((chunks, hv * key_dim), dtype=torch.float32, device=parts.device)
+        chunk_decay = torch.empty((chunks, hk), dtype=torch.float32, device=parts.device)
+    _layer().call("wick_gla_mix", "piiiiiiippffplpipppiiippp", _p(parts), splits, n, cols, heads, key_dim, v_dim, rank, _p(w2), _p(b2),
+                  float(q_scale), float(tau), _p(records), hv * key_dim, _p(batch.slots), batch.n_seqs, _p(batch.cu_seqlens),
+                  _p(qkav), _p(y), max_q, chunk, chunks, _p(chunk_state), _p(chunk_decay), _stream(),
+                  kernels=1 + (3 if chunks else 1))
+    return y
+
+
+def gla_norm_gate(y: torch.Tensor, parts: torch.Tensor, g_col: int, heads: int, v_dim: int, weight: torch.Tensor, eps: float,
+                  dtype: torch.dtype) -> torch.Tensor:
+    """Every head's ``v_dim`` numbers of y (float32 [n, H dv]) divided by their root mean square and multiplied by ``weight``
+    (float32 [dv], shared by the heads), then by silu(g), g the columns from ``g_col`` on of the float32 partial sums
+    ``parts`` [splits, n, cols]; [n, H dv] in ``dtype``."""
+    _cuda("y", y, torch.float32)
+    _cuda("parts", parts, torch.float32)
+    n = y.shape[0]
+    _need(tuple(y.shape) == (n, heads * v_dim), f"y must be [n, {heads * v_dim}]")
+    _need(parts.dim() == 3 and parts.shape[1] == n and parts.shape[2] >= g_col + heads * v_dim, "parts must hold the gate's columns")
+    _cuda("weight", weight, torch.float32, (v_dim,))
+    out = torch.empty((n, heads * v_dim), dtype=dtype, device=y.device)
+    _layer().call(f"wick_gla_norm_gate_{_dt(out)}", "ppiiiiiipfpp", _p(y), _p(parts), parts.shape[0], n, parts.shape[2], int(g_col), heads,
+                  v_dim, _p(weight), float(eps), _p(out), _stream())
+    return out
+
+
+def embed_sinusoid(table: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor], scale: float
+                   ) -> torch.Tensor:
+    """float32 [n, width]: rows of ``table`` at ``tokens`` times ``scale`` plus, with ``freq`` (float32 [ceil(width / 2)]), the
+    positions' vectors: element 2 i gets sin(p freq[i]), element 2 i + 1 the cosine, the angle a float32 product."""
+    _cuda("table", table)
+    n, (vocab, width) = tokens.numel(), table.shape
+    _cuda("tokens", tokens, torch.int32, (n,))
+    _cuda("positions", positions, torch.int32, (n,))
+    if freq is not None:
+        _cuda("freq", freq, torch.float32, ((width + 1) // 2,))
+    out = torch.empty((n, width), dtype=torch.float32, device=table.device)
+    _layer().call(f"wick_embed_sinusoid_{_dt(table)}", "ppppfpiip", _p(table), _p(tokens), _p(positions), _p(freq), float(scale), _p(out),
+                  n, width, _stream())
+    return out
+
+
+def stream_offset_(x: torch.Tensor, x0: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> torch.Tensor:
+    """x <- x + x0 + vec in place (float32 [n, width]; x0 of the same shape or None; vec float32 [width] or None)."""
+    _cuda("x", x, torch.float32)
+    n, width = x.shape
+    if x0 is not None:
+        _cuda("x0", x0, torch.float32, (n, width))
+    if vec is not None:
+        _cuda("vec", vec, torch.float32, (width,))
+    _layer().call("wick_stream_offset", "pppiip", _p(x), _p(x0), _p(vec), n, width, _stream())
+    return x
 
 
 # ---- a state-space recurrence with its short convolution ----------------------------------------------------------------

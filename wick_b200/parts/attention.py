@@ -16,7 +16,9 @@ mixer          ``attention``           width, heads, kv_heads, head_dim, v_dim
                                        qk_norm (None, ``head`` or ``projection``),
                                        eps, position (PartSpec), mask (None or
                                        {"kind": "block" | "window", "size": n}),
-                                       sink, value_blend (None or {"role":
+                                       sink, sink_value (a fixed score of the
+                                       sink instead of learned ones),
+                                       value_blend (None or {"role":
                                        "source" | "blend", "group": key}),
                                        qk_norm_weight (default True),
                                        qk_norm_after_rotation (default False),
@@ -44,7 +46,8 @@ key/value heads, values of size e):
   them, those in p's own block of ``size`` positions (blocks counted from position 0 of the
   sequence, wherever a prompt was cut), or the last ``size``;
 * weights exp(s_j) / (sum_j exp(s_j) + exp(sink_h)): the learned sink of a head adds to the
-  denominator only;
+  denominator only; with ``sink_value`` c every head's sink has the score c and there is no tensor
+  (c = 0: one is added to the denominator);
 * ``gate``: the heads' results, side by side, are multiplied element by element by
   sigmoid(Wg h), a matrix of H e rows that reads the mixer's own input (float32 sigmoid);
 * the heads' results, side by side, go through Wo.
@@ -189,7 +192,8 @@ class Attention(Mixer):
             self.mask, self.mask_size = str(mask["kind"]), int(mask["size"])
             if self.mask not in ("block", "window") or self.mask_size <= 0:
                 raise ValueError(f"a mask is a block or a window of a positive size, not {mask}")
-        self.has_sink = bool(p.get("sink", False))
+        self.sink_value = float(p["sink_value"]) if p.get("sink_value") is not None else None
+        self.has_sink = bool(p.get("sink", False)) and self.sink_value is None
         self.blend = p.get("value_blend")
         if self.blend is not None and self.blend.get("role") not in ("source", "blend"):
             raise ValueError(f"value_blend's role is 'source' or 'blend', not {self.blend}")
@@ -247,6 +251,8 @@ class Attention(Mixer):
             self.q_weight, self.k_weight = hold(fetch(nm["q_norm"]), "vector"), hold(fetch(nm["k_norm"]), "vector")
         if self.has_sink:
             self.sink = hold(fetch(nm["sink"]), "vector")
+        elif self.sink_value is not None:
+            self.sink = torch.full((self.heads,), self.sink_value, dtype=torch.float32, device=self.ctx.device)
         if self.blend is not None:
             self.blend_factor = hold(fetch(nm["blend"]), "vector").reshape(1)
 

@@ -45,7 +45,11 @@ class TensorSpec:
     one), ``unit_interval`` (a blend factor), ``distinct_below`` (integer rows of different
     values below ``init_arg``), ``absent`` (an optional tensor that random models leave out),
     ``conv_taps`` (a short filter's taps, N(0, 1 / taps)), ``router`` (rows whose scores differ
-    from token to token), ``mix_pair`` (a matrix [w, 2 w] near the sum of its two halves' inputs)."""
+    from token to token), ``mix_pair`` (a matrix [w, 2 w] near the sum of its two halves' inputs), ``decay_out`` and
+    ``decay_bias`` (the second step and the bias of a decay's logits).
+
+    A size of -1 in ``shape`` is whatever the checkpoint has there (the part checks it against its other tensors when it
+    loads); random weights take ``init_arg`` for it."""
 
     name: str
     shape: Tuple[int, ...]
@@ -274,16 +278,19 @@ class SideInput(Part):
     the stream alone."""
     category = "side"
 
-    def forward(self, h: Hidden, batch: "Any") -> None:
+    def forward(self, h: Hidden, batch: "Any", index: int = 0) -> None:
         """``h`` comes with everything of the layer added or pending; the part leaves
-        its own addition in ``h`` (added, or pending through :meth:`Hidden.defer`)."""
+        its own addition in ``h`` (added, or pending through :meth:`Hidden.defer`).  ``index``:
+        the number a schedule entry gives a shared part that runs before it (which pass begins)."""
         raise NotImplementedError
 
 
 class Embedding(Part):
     category = "embedding"
 
-    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+    NEEDS_POSITIONS = False      # True: forward is also given the tokens' positions (int32 [n])
+
+    def forward(self, tokens: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         """int32 [n] -> float32 [n, width]."""
         raise NotImplementedError
 

@@ -7,7 +7,13 @@ side           ``gated_token_rows``    width, dim, offset, eps, table (the place
                                        of the model's shared table part), names
                                        (gate, proj, norm -> local names)
 side           ``mix_with_embedding``  width, tensor (local name of the matrix)
+side           ``pass_offset``         width, passes, add_embedding, tensor (local
+                                       name of the [passes, width] vectors)
 =============  ======================  ==========================================
+
+``pass_offset`` (a shared part that a schedule entry names in ``before``, with the number t of the pass as its index):
+x <- x + x0 + s_t, where x0, the embedding's output for the same token, is added before every pass but the first (with
+``add_embedding``) and s_t is row t of the part's tensor.  float32, one kernel.
 
 ``mix_with_embedding`` (a shared part that a schedule entry names in ``before``): with x the stream
 and x0 the embedding's output for the same token, x <- W [x; x0], W of shape [width, 2 width] with the
@@ -73,7 +79,7 @@ class GatedTokenRows(SideInput):
     def weight_bytes(self):
         return self.gate.weight_bytes() + self.proj.weight_bytes() + 4 * self.width
 
-    def forward(self, h, batch):
+    def forward(self, h, batch, index=0):
         dt = self.ctx.dtype
         h.resolved(dt)                                               # x with the layer's sums, and its copy in h.act
         z = self.gate.forward(h.act, torch.float32)                  # [n, dim]
@@ -103,7 +109,7 @@ class MixWithEmbedding(SideInput):
     def weight_bytes(self):
         return self.mix.weight_bytes()
 
-    def forward(self, h, batch):
+    def forward(self, h, batch, index=0):
         x0 = batch.memo.get("embedding_output")
         if x0 is None:
             raise RuntimeError("the step's memo holds no embedding output")
@@ -114,5 +120,41 @@ class MixWithEmbedding(SideInput):
         h.defer(None)
 
 
+class PassOffset(SideInput):
+    PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.passes = int(params["width"]), int(params["passes"])
+        self.add_embedding = bool(params.get("add_embedding", True))
+        self.NEEDS_EMBEDDING_OUTPUT = self.add_embedding   # the model leaves the embedding's output in the step's memo
+        self.name = str(params.get("tensor", "weight"))
+        self.steps = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.passes, self.width), "vector", init="around_zero")]
+
+    def load(self, fetch):
+        self.steps = self.ctx.hold(fetch(self.name), "vector")
+
+    def tensor(self, name):
+        return self.steps if name == self.name else None
+
+    def weight_bytes(self):
+        return 4 * self.width
+
+    def forward(self, h, batch, index=0):
+        if not 0 <= index < self.passes:
+            raise ValueError(f"pass {index} of {self.passes}")
+        x0 = None
+        if self.add_embedding and index > 0:
+            x0 = batch.memo.get("embedding_output")
+            if x0 is None:
+                raise RuntimeError("the step's memo holds no embedding output")
+        ops.stream_offset_(h.resolved(), x0, self.steps[index])
+        h.act = None
+
+
+register_part("side", "pass_offset", PassOffset)
 register_part("side", "gated_token_rows", GatedTokenRows)
 register_part("side", "mix_with_embedding", MixWithEmbedding)

@@ -23,7 +23,10 @@ block          ``prenorm_residual``    width and layer_scale (mixer, ffn -> loca
                                        (mixer, ffn -> local names, eps) where
                                        they are normed before the sum
 block          ``postnorm_residual``   alpha
-embedding      ``table``               vocab, width, tensor
+embedding      ``table``               vocab, width, tensor, scale (a factor of
+                                       the rows, default 1), position (None or
+                                       {"kind": "sinusoid", "base": b}: a vector
+                                       per position that is added)
 head           ``linear``              vocab, width, tied, tensor, soft_cap
 =============  ======================  ==========================================
 
@@ -499,6 +502,10 @@ class PostNormResidual(Block):
 
 # ---------------------------------------------------------------------------
 class TableEmbedding(Embedding):
+    """x = table[token] * scale (+ the position's vector).  ``position`` of kind ``sinusoid``: element 2 i of position p's
+    vector is sin(p base^(-2i/width)), element 2 i + 1 the cosine of the same angle; the frequencies are evaluated in
+    float64 and rounded to float32 once, the angle is their float32 product with the position."""
+
     PROMPT_CAPTURABLE = True
 
     def __init__(self, params, ctx):
@@ -506,6 +513,16 @@ class TableEmbedding(Embedding):
         self.vocab, self.width = int(params["vocab"]), int(params["width"])
         self.name = str(params.get("tensor", "weight"))
         self.weight: Optional[torch.Tensor] = None
+        self.scale = float(params.get("scale", 1.0))
+        pos = params.get("position")
+        self.freq: Optional[torch.Tensor] = None
+        if pos is not None:
+            if pos.get("kind") != "sinusoid":
+                raise ValueError(f"an embedding's position vectors are of kind 'sinusoid', not {pos.get('kind')!r}")
+            base, w = float(pos.get("base", 10000.0)), self.width
+            f = [base ** (-2.0 * i / w) for i in range((w + 1) // 2)]
+            self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(ctx.device)
+        self.NEEDS_POSITIONS = self.freq is not None or self.scale != 1.0
 
     def tensor_specs(self):
         return [TensorSpec(self.name, (self.vocab, self.width))]
@@ -516,7 +533,9 @@ class TableEmbedding(Embedding):
     def tensor(self, name):
         return self.weight if name in (self.name, "weight") else None
 
-    def forward(self, tokens):
+    def forward(self, tokens, positions=None):
+        if self.NEEDS_POSITIONS:
+            return ops.embed_sinusoid(self.weight, tokens, positions, self.freq, self.scale)
         return ops.embed(self.weight, tokens)
 
     def weight_bytes(self):

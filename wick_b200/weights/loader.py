@@ -4,7 +4,7 @@ Every problem of a checkpoint is collected and reported in ONE error: tensors
 the model needs and the files lack, tensors the files carry and the model does
 not know, and tensors of the wrong shape (wording after wick
 ``src/model.rs:137-140,180-183``: "missing tensor NAME", "NAME: expected shape
-[r, c], found [...]").  bf16 stays bf16, f16 goes through f32 to bf16, f32 is
+[r, c], found [...]"; a size a part declares as -1 is whatever the file has, and the part checks it against its other tensors when it loads).  bf16 stays bf16, f16 goes through f32 to bf16, f32 is
 rounded to bf16 for matrices of the bfloat16 path and kept for everything the
 parts declare as 32-bit (``src/model.rs:64-85,136-142``).
 """
@@ -42,7 +42,7 @@ def check_tensors(model: Model, st: SafeTensorsDir) -> None:
                 missing.append(name)
                 lines.append(f"missing tensor {name}")
             continue
-        if tuple(info.shape) != tuple(ts.shape):
+        if len(info.shape) != len(ts.shape) or any(want != -1 and have != want for have, want in zip(info.shape, ts.shape)):
             wrong.append(name)
             lines.append(f"{name}: expected shape {list(ts.shape)}, found {list(info.shape)}")
         elif ts.role in ("matrix", "vector") and info.dtype_name not in _FLOAT_FILE_DTYPES:

@@ -32,6 +32,7 @@ def _seed_for(seed: int, name: str) -> int:
 def _make(name: str, ts, seed: int, device, dtype: torch.dtype, std: float, vector_std: float) -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_seed_for(seed, name))
+    shape = tuple(ts.init_arg if d == -1 else d for d in ts.shape)      # (a size the checkpoint decides: the part's choice for random weights)
     if ts.role == "table":
         if ts.init != "distinct_below" or len(ts.shape) != 2 or ts.shape[1] > ts.init_arg:
             raise ValueError(f"{name}: no random rule for this integer table")
@@ -40,7 +41,7 @@ def _make(name: str, ts, seed: int, device, dtype: torch.dtype, std: float, vect
         return keys.argsort(dim=1)[:, :ts.shape[1]].to(torch.int32).contiguous()
     if ts.init == "unit_interval":
         return (0.2 + 0.6 * torch.rand(ts.shape, generator=g, device=device, dtype=torch.float32)).to(dtype)
-    t = torch.randn(ts.shape, generator=g, device=device, dtype=torch.float32)
+    t = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
     if ts.init == "conv_taps":                         # a short filter: taps that add up to something of the input's size
         t = t / float(ts.shape[-1]) ** 0.5
     elif ts.init == "router":                          # scores that differ from token to token
@@ -51,6 +52,10 @@ def _make(name: str, ts, seed: int, device, dtype: torch.dtype, std: float, vect
         eye = torch.eye(ts.shape[0], half, device=device, dtype=torch.float32)
         t[:, :half] += 0.7 * eye
         t[:, half:2 * half] += 0.7 * eye
+    elif ts.init == "decay_out":                       # the second step of a decay's projection: logits that differ from token to token
+        t = 4.0 * t
+    elif ts.init == "decay_bias":                      # logits whose sigmoid lies mostly above one half
+        t = 1.0 + t
     elif ts.init == "around_zero":
         t = vector_std * t
     elif ts.role == "vector":
