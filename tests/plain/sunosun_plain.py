@@ -171,7 +171,7 @@ def forward(cfg: dict, t: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in t.items()}
     eps = cfg["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    x0 = embed(tokens, t["embed"], cfg["embedding"]["scale"])
+    x0 = embed(tokens, t["embed"], (cfg.get("embedding") or {}).get("scale", 1.0))
     x = x0.clone()
     for i, begins in run_order(cfg):
         if begins is not None:
