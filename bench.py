@@ -2,7 +2,7 @@
 """Decode and prefill throughput of wick_b200 on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--model 8b|14b|32b]
-    python bench.py --design nibotar|tuguvik|fasunex [--design-size 2k|4k]      (a line of its own, see below)
+    python bench.py --design nibotar|tuguvik|fasunex|sunosun [--design-size 2k|4k]      (a line of its own, see below)
 
 The default run has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32
 heads over 8 kv heads of 128, intermediate 12288, vocabulary 151936) with random
@@ -38,6 +38,11 @@ bytes, so that every kind can be held against the measured peaks.
 ``--design fasunex`` prints the line of the Fasunex design (layers that alternate between a chunked attention beside a
 state-space recurrence and an attention whose keys are its values, routed experts with identity outputs) beside Nibotar,
 the closest design here, at equal size, with the same kind of ``parts``.
+``--design sunosun`` prints the line of the Sunosun design (layers that alternate between a softmax attention beside a gated
+linear attention and a gated linear attention alone; one-matrix experts chosen within groups, with a gated shared expert)
+beside Fasunex, the closest design here (its parallel mixer holds a state-space recurrence with a state of the same size),
+at equal size, with the same kind of ``parts``; the recurrences' scans are also held against the float32 rate of the CUDA
+cores, since that, not memory, bounds them in a prompt.
 """
 import argparse
 import json
@@ -268,6 +273,8 @@ def design_step_bytes(eng, z, name, batch, kv_tokens):
         kv_tokens = min(kv_tokens, batch * (z["window"] + z["keep_first"]))
     if name == "fasunex":
         return fasunex_step_bytes(eng, z, batch, kv_tokens)
+    if name == "sunosun":
+        return sunosun_step_bytes(eng, z, batch, kv_tokens)
     return n + eng.cache.read_bytes(int(kv_tokens), batch)
 
 
@@ -549,7 +556,10 @@ def tuguvik_parts(torch, wick, pk, z, name, cfg_json):
             us = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e3
             fl, by = sum(e[2] for e in evs), sum(e[3] for e in evs)
             r = res[kind] = {"us_per_step": us, "calls": len(evs)}
-            if fl:
+            if fl and kind.startswith("recurrence ("):
+                r["fp32_tflops"] = fl / (us * 1e-6) / 1e12
+                r["fp32_frac_of_nominal"] = r["fp32_tflops"] / FP32_TFLOPS_NOMINAL
+            elif fl:
                 r["tflops"] = fl / (us * 1e-6) / 1e12
                 r["tflops_frac"] = r["tflops"] / pk["bf16_tflops"]
             r["gbs"] = by / (us * 1e-6) / 1e9
@@ -613,6 +623,9 @@ def tuguvik_compare(args) -> int:
 # heads, layers, vocabulary, block size and experts.  Layers alternate between the parallel mixer (chunked attention beside
 # a state-space recurrence of `ssm_heads` x `ssm_dim` numbers with a state of `ssm_state`) and the attention whose keys are
 # its values; every layer has routed experts with two identity outputs.
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12      # 148 SMs x 128 lanes x one multiply-add a cycle at 1965 MHz
+
+
 def fasunex_configs(z):
     d = z["dim"]
     left = dict(heads=z["heads"], kv_heads=z["kv"], dim=d, vdim=d, scale=d ** -0.5, mask={"size": z["mask"]},
@@ -688,21 +701,31 @@ def fasunex_parts(torch, wick, pk, z, name, cfg_json):
         H, Pn, N = k["heads"], k["head_dim"], k["state"]
         ch = H * Pn + 2 * k["groups"] * N
         rec = 2 * 4 * k["batch"].n_seqs * (H * Pn * N + (k["taps"] - 1) * ch)
-        return 0.0, nbytes(parts) + 4 * n * (2 * ch + H * Pn) + rec
+        # (two multiply-adds per number of the state and token: the update and the read-out)
+        return 4.0 * n * H * Pn * N, nbytes(parts) + 4 * n * (2 * ch + H * Pn) + rec
+
+    def gla_work(r, parts, **k):
+        n = parts.shape[1]
+        H, dk, dv = k["heads"], k["key_dim"], k["v_dim"]
+        rec = 2 * 4 * k["batch"].n_seqs * H * dk * dv
+        return 4.0 * n * H * dk * dv, nbytes(parts, r) + 2 * 4 * n * (3 * H * dk + H * dv) + rec
 
     def norm_work(r, x, delta=None, *a, **k):
         return 0.0, nbytes(x, delta) + (nbytes(x) if delta is not None and k.get("rows") is None else 0) + (nbytes(r) if r is not None and r is not x else 0)
 
-    def ffn_work(width, ff, top, share, shared_ff):
+    def ffn_work(width, ff, top, share, shared_ff, mats=3, shared_mats=3):
         def work(r, x, *a, **k):
             n = x.shape[0]
-            act = top * share * ff + shared_ff
-            return 2.0 * n * 3 * width * act, nbytes(x, r) + min(n * top, z["experts"]) * 3 * width * ff * 2 + 3 * width * shared_ff * 2
+            act = mats * top * share * ff + shared_mats * shared_ff
+            return (2.0 * n * width * act,
+                    nbytes(x, r) + min(n * top, z["experts"]) * mats * width * ff * 2 + shared_mats * width * shared_ff * 2)
         return work
 
     for fname, kind, work in (("attention_masked", "attention", attn_work), ("qkv_finish", "finish", rows_work),
                               ("gate_rows_", "output gate", rows_work), ("ssm_mix", "recurrence (convolution, scan)", ssm_work),
                               ("ssm_gate_norm", "recurrence's gate and norm", rows_work), ("weighted_sum", "sum of the branches", rows_work),
+                              ("gla_mix", "recurrence (decays, scan)", gla_work), ("gla_norm_gate", "recurrence's gate and norm", rows_work),
+                              ("embed_sinusoid", "embedding", rows_work),
                               ("concat_activation", "pass input", rows_work), ("stream_update", "norm", norm_work),
                               ("scaled_add_rmsnorm", "norm", lambda r, x, delta, *a, **k: norm_work(r, x, delta)),
                               ("rmsnorm", "norm", lambda r, x, *a, **k: norm_work(r, x, k.get("delta"), rows=k.get("rows")))):
@@ -716,7 +739,8 @@ def fasunex_parts(torch, wick, pk, z, name, cfg_json):
                     product(kind, getattr(m, attr))
         f = blk.ffn
         if type(f).__name__ == "RoutedMoE":
-            work = ffn_work(W, f.intermediate, f.top, f.experts / float(f.outputs), 0)
+            sh = f.shared.intermediate if f.shared is not None else 0
+            work = ffn_work(W, f.intermediate, f.top, f.experts / float(f.outputs), sh, 3 if f.gated else 2, 2)
         elif type(f).__name__ == "TableMoE":
             work = ffn_work(W, f.intermediate, f.top, 1.0, z["shared_ff"])
         else:
@@ -730,7 +754,10 @@ def fasunex_parts(torch, wick, pk, z, name, cfg_json):
             us = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e3
             fl, by = sum(e[2] for e in evs), sum(e[3] for e in evs)
             r = res[kind] = {"us_per_step": us, "calls": len(evs)}
-            if fl:
+            if fl and kind.startswith("recurrence ("):
+                r["fp32_tflops"] = fl / (us * 1e-6) / 1e12
+                r["fp32_frac_of_nominal"] = r["fp32_tflops"] / FP32_TFLOPS_NOMINAL
+            elif fl:
                 r["tflops"] = fl / (us * 1e-6) / 1e12
                 r["tflops_frac"] = r["tflops"] / pk["bf16_tflops"]
             r["gbs"] = by / (us * 1e-6) / 1e9
@@ -790,6 +817,69 @@ def fasunex_compare(args) -> int:
     return 0 if all(m["finite"] for m in models.values()) else 1
 
 
+# ---- --design sunosun ----------------------------------------------------------
+# Sunosun beside Fasunex, the closest design here (a softmax attention beside a recurrence in one mixer, routed experts): the
+# same width, heads, layers, vocabulary and experts.  Layers alternate between the parallel mixer (attention with biases and a
+# sink of score 0 beside a gated linear attention of width / 128 heads with 128 key channels and 128 values, a state as large as
+# Fasunex's recurrence) and a gated linear attention alone.  The experts have two matrices where Fasunex's have three, so
+# their inner size is half as large again; every layer has the shared expert.
+def sunosun_configs(z):
+    d = z["dim"]
+    left = dict(heads=z["heads"], kv_heads=z["kv"], dim=d, vdim=d, scale=d ** -0.5)
+    right = dict(heads=z["width"] // 128, dim=128, vdim=128, tau=16.0)
+    mlp = {"kind": "moe", "expert": {"ff": z["expert_ff"] * 3 // 2}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    layers = [dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=mlp) if i % 2 == 0
+              else dict(type="gla", mixer=right, mlp=mlp) for i in range(z["layers"])]
+    suno = dict(architecture="Sunosun", vocab=z["vocab"], width=z["width"], norm={"eps": 1e-5}, embedding={"scale": 1.0},
+                logit_softcap=30.0, layers=layers)
+    return {"sunosun": suno, "fasunex": fasunex_configs(z)["fasunex"]}
+
+
+def sunosun_step_bytes(eng, z, batch, kv_tokens):
+    """Bytes a decode step of Sunosun has to read: the weights (of a layer's experts a batch uses E (1 - (1 - top / E)^batch)
+    on average), the keys and values of the layers that have an attention, and the recurrences' records (read and written)."""
+    n = eng.model.weight_bytes_per_step()
+    e, top = z["experts"], z["top"]
+    one = 2 * (z["expert_ff"] * 3 // 2) * z["width"] * 2
+    n += z["layers"] * (e * (1.0 - (1.0 - top / e) ** batch) - min(top, e)) * one
+    n += (z["layers"] - z["layers"] // 2) * kv_tokens * 2 * z["kv"] * z["dim"] * 2
+    for g in eng.cache.groups:
+        if g.need.kind == "state":
+            n += 2 * g.store.read_bytes(0, batch)
+    return n
+
+
+def sunosun_compare(args) -> int:
+    import torch
+    import wick_b200 as wick
+    pk = peaks()
+    z = DESIGN_SIZES[args.design_size]
+    cfgs = sunosun_configs(z)
+    if args.design_parts:
+        print(json.dumps({args.design_parts: fasunex_parts(torch, wick, pk, z, args.design_parts, cfgs[args.design_parts])}))
+        return 0
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+    with Clocks() as clk:
+        models = {name: design_model(torch, wick, pk, z, name, cfgs[name], steps, warmup) for name in ("sunosun", "fasunex")}
+    env = dict(os.environ, WICK_B200_NO_PDL="1")
+    parts, errors = {}, {}
+    for name in ("sunosun", "fasunex"):                # (a process each: the timing wrappers replace the module's functions)
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", "sunosun", "--design-size", args.design_size,
+                            "--design-parts", name], env=env, capture_output=True, text=True)
+        for ln in r.stdout.splitlines():
+            if ln.startswith("{"):
+                parts.update(json.loads(ln))
+        if name not in parts:
+            errors[name] = r.stderr[-600:]
+    line = {"metric": f"Sunosun beside Fasunex at equal size ({args.design_size}): prefill and decode tok/s, bf16", "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "sizes": z,
+            "data": "synthetic: seeded random weights, seeded uniform random token ids", "models": models, "parts": parts,
+            "parts_error": errors or None, "clocks": clk.result, "peaks": pk, "fp32_tflops_nominal": FP32_TFLOPS_NOMINAL}
+    print(json.dumps(line))
+    return 0 if all(m["finite"] for m in models.values()) else 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -810,8 +900,8 @@ def main() -> int:
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-decode", action="store_true", help="prefill only (for profiling)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
-    ap.add_argument("--design", default=None, choices=["nibotar", "tuguvik", "fasunex"],
-                    help="another line: this design beside Qwen3 (fasunex: beside Nibotar) at equal size")
+    ap.add_argument("--design", default=None, choices=["nibotar", "tuguvik", "fasunex", "sunosun"],
+                    help="another line: this design beside Qwen3 (fasunex: beside Nibotar; sunosun: beside Fasunex) at equal size")
     ap.add_argument("--design-size", default="2k", choices=sorted(DESIGN_SIZES))
     ap.add_argument("--design-parts", nargs="?", const="both", default=None,
                     help="only the per-kernel times of --design (run by --design itself; tuguvik: of the model named)")
@@ -822,6 +912,8 @@ def main() -> int:
         return tuguvik_compare(args)
     if args.design == "fasunex":
         return fasunex_compare(args)
+    if args.design == "sunosun":
+        return sunosun_compare(args)
     if args.design:
         return design_compare(args)
     if args.gpus != 1:

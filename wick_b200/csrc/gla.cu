@@ -52,32 +52,61 @@ __device__ __forceinline__ float gla_sum_parts(const float* __restrict__ parts, 
     return v;
 }
 
-// One block per token.  out row: [q * q_scale | k | a | v], 3 H dk + H dv numbers.
-__global__ void __launch_bounds__(256)
+constexpr int GLA_PREP_THREADS = 256;             // channels a block of the preparation takes
+constexpr int GLA_PREP_RANK = 32;                 // a thread keeps its row of W2 in registers up to this rank
+
+// grid (ceil(tokens / per_block), ceil(H dk / 256) + ceil(H dv / 256)): a block takes 256 key channels (q, k and the decay) or
+// 256 value elements of `per_block` tokens in turn, so that a thread's row of W2 is read once for all of them.  out row:
+// [q * q_scale | k | a | v], 3 H dk + H dv numbers.
+__global__ void __launch_bounds__(GLA_PREP_THREADS)
 gla_prepare_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int cols, int HK, int HV, int rank,
                    const float* __restrict__ w2, const float* __restrict__ b2, float q_scale, float inv_tau,
-                   float* __restrict__ out) {
-    extern __shared__ float low[];                                       // [rank]
+                   float* __restrict__ out, int n, int per_block) {
+    extern __shared__ float low[];                                       // [per_block][rank]
     pdl_trigger();
     pdl_wait();
     parts = fresh(parts);
-    const int t = blockIdx.x, tid = threadIdx.x;
-    const int64_t row = (int64_t)t * cols;
+    const int tid = threadIdx.x, t0 = blockIdx.x * per_block, nt = min(per_block, n - t0);
+    const int tiles_k = (HK + GLA_PREP_THREADS - 1) / GLA_PREP_THREADS;
     const int low_col = 2 * HK + 2 * HV, channels = 3 * HK + HV;
-    for (int j = tid; j < rank; j += blockDim.x) low[j] = gla_sum_parts(parts, splits, split_stride, row + low_col + j);
+    if ((int)blockIdx.y >= tiles_k) {
+        const int c = ((int)blockIdx.y - tiles_k) * GLA_PREP_THREADS + tid;
+        if (c < HV)
+            for (int i = 0; i < nt; ++i)
+                out[(int64_t)(t0 + i) * channels + 3 * HK + c] = gla_sum_parts(parts, splits, split_stride, (int64_t)(t0 + i) * cols + 2 * HK + c);
+        return;
+    }
+    for (int idx = tid; idx < nt * rank; idx += GLA_PREP_THREADS) {
+        const int i = idx / rank, j = idx - i * rank;
+        low[idx] = gla_sum_parts(parts, splits, split_stride, (int64_t)(t0 + i) * cols + low_col + j);
+    }
     __syncthreads();
-    float* o = out + (int64_t)t * channels;
-    for (int c = tid; c < HK; c += blockDim.x) {
+    const int c = blockIdx.y * GLA_PREP_THREADS + tid;
+    if (c >= HK) return;
+    const float* wr = w2 + (int64_t)c * rank;
+    const float bias = b2 ? b2[c] : 0.f;
+    const bool held = rank <= GLA_PREP_RANK;
+    float w[GLA_PREP_RANK];
+#pragma unroll
+    for (int j = 0; j < GLA_PREP_RANK; ++j) w[j] = (held && j < rank) ? wr[j] : 0.f;
+    for (int i = 0; i < nt; ++i) {
+        const int64_t row = (int64_t)(t0 + i) * cols;
+        const float* li = low + i * rank;
+        float z = bias;
+        if (held) {
+#pragma unroll
+            for (int j = 0; j < GLA_PREP_RANK; ++j)
+                if (j < rank) z = fmaf(w[j], li[j], z);
+        } else {
+            for (int j = 0; j < rank; ++j) z = fmaf(wr[j], li[j], z);
+        }
+        float* o = out + (int64_t)(t0 + i) * channels;
         o[c] = gla_sum_parts(parts, splits, split_stride, row + c) * q_scale;
         o[HK + c] = gla_sum_parts(parts, splits, split_stride, row + HK + c);
-        float z = b2 ? b2[c] : 0.f;
-        const float* wr = w2 + (int64_t)c * rank;
-        for (int j = 0; j < rank; ++j) z = fmaf(wr[j], low[j], z);
         // log sigmoid(z) = -softplus(-z)
         const float sp = -z > 20.0f ? -z : log1pf(expf(-z));
         o[2 * HK + c] = expf(-sp * inv_tau);
     }
-    for (int c = tid; c < HV; c += blockDim.x) o[3 * HK + c] = gla_sum_parts(parts, splits, split_stride, row + 2 * HK + c);
 }
 
 // The sums of four columns over the LN threads that share them (see the state-space scan: the same exchange).
@@ -344,7 +373,7 @@ gla_chunk_join_kernel(float* __restrict__ chunk_state, const float* __restrict__
     *rec = S;
 }
 
-// One block per token, a warp per head in turn: o / sqrt(mean(o^2) + eps) * w * silu(g), g from the projection's sums.
+// grid (tokens, groups of heads), a warp per head: o / sqrt(mean(o^2) + eps) * w * silu(g), g from the projection's sums.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gla_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ parts, int splits, int64_t split_stride, int cols,
@@ -353,8 +382,8 @@ gla_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ part
     pdl_wait();
     y = fresh(y);
     parts = fresh(parts);
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    for (int h = warp; h < H; h += n_warps) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5, warp = blockIdx.y * n_warps + (threadIdx.x >> 5);
+    for (int h = warp; h < H; h += n_warps * gridDim.y) {
         const float* row = y + ((int64_t)t * H + h) * P;
         float ss = 0.f;
         for (int j = lane; j < P; j += 32) ss = fmaf(row[j], row[j], ss);
@@ -422,8 +451,11 @@ WICK_API int wick_gla_mix(const float* parts, int splits, int n, int cols, int H
     WICK_REQUIRE((size_t)rank * 4 <= 48 * 1024, "gla_mix: a rank of %d is beyond one block's shared memory", rank);
     if (n == 0 || n_seqs == 0) return 0;
     const int64_t stride = (int64_t)n * cols;
-    WICK_CUDA(launch(gla_prepare_kernel, dim3(n), dim3(256), (size_t)rank * 4, s, parts, splits, stride, cols, HK, HV, rank, w2, b2,
-                     q_scale, 1.0f / tau, qkav));
+    // (long steps: eight tokens a block share a thread's row of W2; short ones: a block a token, for more blocks)
+    const int per_block = (n >= 512 && (size_t)rank * 8 * 4 <= 48 * 1024) ? 8 : 1;
+    WICK_CUDA(launch(gla_prepare_kernel, dim3(ceil_div(n, per_block), ceil_div(HK, GLA_PREP_THREADS) + ceil_div(HV, GLA_PREP_THREADS)),
+                     dim3(GLA_PREP_THREADS), (size_t)per_block * rank * 4, s, parts, splits, stride, cols, HK, HV, rank, w2, b2, q_scale,
+                     1.0f / tau, qkav, n, per_block));
     if (check_launch("gla_prepare")) return 1;
     const int N = dk, P = dv;
     int ln = 1;
@@ -457,8 +489,9 @@ WICK_API int wick_gla_mix(const float* parts, int splits, int n, int cols, int H
                       float eps, void* out, void* s) {                                                                         \
         WICK_REQUIRE(H > 0 && dv > 0 && g_col >= 0 && g_col + H * dv <= cols, "gla_norm_gate: bad sizes");                     \
         if (n == 0) return 0;                                                                                                  \
-        WICK_CUDA(launch(gla_norm_gate_kernel<T>, dim3(n), dim3(H >= 8 ? 256 : 32 * H), 0, (cudaStream_t)s, y, parts, splits,  \
-                         (int64_t)n * cols, cols, g_col, H, dv, w, eps, (T*)out));                                              \
+        const int warps = H >= 4 ? 4 : H;                                                                                      \
+        WICK_CUDA(launch(gla_norm_gate_kernel<T>, dim3(n, ceil_div(H, warps)), dim3(32 * warps), 0, (cudaStream_t)s, y, parts, \
+                         splits, (int64_t)n * cols, cols, g_col, H, dv, w, eps, (T*)out));                                      \
         return check_launch("gla_norm_gate");                                                                                  \
     }
 WICK_GLA_NORM_GATE(wick_gla_norm_gate_bf16, bf16)
