@@ -55,42 +55,69 @@ __device__ __forceinline__ float gla_sum_parts(const float* __restrict__ parts, 
 constexpr int GLA_PREP_THREADS = 256;             // channels a block of the preparation takes
 constexpr int GLA_PREP_RANK = 32;                 // a thread keeps its row of W2 in registers up to this rank
 
-// grid (ceil(tokens / per_block), ceil(H dk / 256) + ceil(H dv / 256)): a block takes 256 key channels (q, k and the decay) or
-// 256 value elements of `per_block` tokens in turn, so that a thread's row of W2 is read once for all of them.  out row:
-// [q * q_scale | k | a | v], 3 H dk + H dv numbers.
+// grid (ceil(tokens / PB), ceil(H dk / 256) + ceil(H dv / 256)): a block takes 256 key channels (q, k and the decay) or 256
+// value elements of PB tokens, so that a thread's row of W2 is read once for all of them and its PB tokens' numbers are on
+// their way from memory at once.  out row: [q * q_scale | k | a | v], 3 H dk + H dv numbers.
+template <int PB, bool ONE>
 __global__ void __launch_bounds__(GLA_PREP_THREADS)
 gla_prepare_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int cols, int HK, int HV, int rank,
                    const float* __restrict__ w2, const float* __restrict__ b2, float q_scale, float inv_tau,
-                   float* __restrict__ out, int n, int per_block) {
-    extern __shared__ float low[];                                       // [per_block][rank]
+                   float* __restrict__ out, int n, int stage) {
+    extern __shared__ float low[];                                       // [PB][rank], then (stage) the block's rows of W2
     pdl_trigger();
     pdl_wait();
     parts = fresh(parts);
-    const int tid = threadIdx.x, t0 = blockIdx.x * per_block, nt = min(per_block, n - t0);
+    // (ONE: the projection came as one sum; a plain load each, so that a thread's loads are all on their way before the first is used)
+    auto ld = [&](int64_t at) { return ONE ? parts[at] : gla_sum_parts(parts, splits, split_stride, at); };
+    const int tid = threadIdx.x, t0 = blockIdx.x * PB, nt = min(PB, n - t0);
     const int tiles_k = (HK + GLA_PREP_THREADS - 1) / GLA_PREP_THREADS;
     const int low_col = 2 * HK + 2 * HV, channels = 3 * HK + HV;
     if ((int)blockIdx.y >= tiles_k) {
         const int c = ((int)blockIdx.y - tiles_k) * GLA_PREP_THREADS + tid;
-        if (c < HV)
-            for (int i = 0; i < nt; ++i)
-                out[(int64_t)(t0 + i) * channels + 3 * HK + c] = gla_sum_parts(parts, splits, split_stride, (int64_t)(t0 + i) * cols + 2 * HK + c);
+        if (c >= HV) return;
+        float v[PB];
+#pragma unroll
+        for (int i = 0; i < PB; ++i) v[i] = i < nt ? ld((int64_t)(t0 + i) * cols + 2 * HK + c) : 0.f;
+#pragma unroll
+        for (int i = 0; i < PB; ++i)
+            if (i < nt) out[(int64_t)(t0 + i) * channels + 3 * HK + c] = v[i];
         return;
+    }
+    const int c = blockIdx.y * GLA_PREP_THREADS + tid;
+    float qv[PB], kv[PB];
+#pragma unroll
+    for (int i = 0; i < PB; ++i) {
+        const bool in = i < nt && c < HK;
+        const int64_t row = (int64_t)(t0 + i) * cols;
+        qv[i] = in ? ld(row + c) : 0.f;
+        kv[i] = in ? ld(row + HK + c) : 0.f;
     }
     for (int idx = tid; idx < nt * rank; idx += GLA_PREP_THREADS) {
         const int i = idx / rank, j = idx - i * rank;
-        low[idx] = gla_sum_parts(parts, splits, split_stride, (int64_t)(t0 + i) * cols + low_col + j);
+        low[idx] = ld((int64_t)(t0 + i) * cols + low_col + j);
+    }
+    // The block's 256 rows of W2 lie together in memory: they come in whole lines and wait in shared memory, a row's
+    // numbers an odd count apart (thread c then reads row c without meeting its neighbours' banks).
+    float* wt = low + PB * rank;
+    const int ws = rank | 1, c0 = blockIdx.y * GLA_PREP_THREADS;
+    if (stage) {
+        const int64_t most = (int64_t)(HK - c0) * rank;
+        for (int idx = tid; idx < GLA_PREP_THREADS * rank && idx < most; idx += GLA_PREP_THREADS) {
+            const int r = idx / rank;
+            wt[r * ws + (idx - r * rank)] = w2[(int64_t)c0 * rank + idx];
+        }
     }
     __syncthreads();
-    const int c = blockIdx.y * GLA_PREP_THREADS + tid;
     if (c >= HK) return;
-    const float* wr = w2 + (int64_t)c * rank;
+    const float* wr = stage ? wt + tid * ws : w2 + (int64_t)c * rank;
     const float bias = b2 ? b2[c] : 0.f;
     const bool held = rank <= GLA_PREP_RANK;
     float w[GLA_PREP_RANK];
 #pragma unroll
     for (int j = 0; j < GLA_PREP_RANK; ++j) w[j] = (held && j < rank) ? wr[j] : 0.f;
-    for (int i = 0; i < nt; ++i) {
-        const int64_t row = (int64_t)(t0 + i) * cols;
+#pragma unroll
+    for (int i = 0; i < PB; ++i) {
+        if (i >= nt) break;
         const float* li = low + i * rank;
         float z = bias;
         if (held) {
@@ -101,8 +128,8 @@ gla_prepare_kernel(const float* __restrict__ parts, int splits, int64_t split_st
             for (int j = 0; j < rank; ++j) z = fmaf(wr[j], li[j], z);
         }
         float* o = out + (int64_t)(t0 + i) * channels;
-        o[c] = gla_sum_parts(parts, splits, split_stride, row + c) * q_scale;
-        o[HK + c] = gla_sum_parts(parts, splits, split_stride, row + HK + c);
+        o[c] = qv[i] * q_scale;
+        o[HK + c] = kv[i];
         // log sigmoid(z) = -softplus(-z)
         const float sp = -z > 20.0f ? -z : log1pf(expf(-z));
         o[2 * HK + c] = expf(-sp * inv_tau);
@@ -374,7 +401,7 @@ gla_chunk_join_kernel(float* __restrict__ chunk_state, const float* __restrict__
 }
 
 // grid (tokens, groups of heads), a warp per head: o / sqrt(mean(o^2) + eps) * w * silu(g), g from the projection's sums.
-template <typename T>
+template <typename T, bool ONE>
 __global__ void __launch_bounds__(256)
 gla_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ parts, int splits, int64_t split_stride, int cols,
                      int g_col, int H, int P, const float* __restrict__ w, float eps, T* __restrict__ out) {
@@ -390,7 +417,8 @@ gla_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ part
         ss = warp_sum(ss);
         const float f = 1.0f / sqrtf(ss / (float)P + eps);
         for (int j = lane; j < P; j += 32) {
-            const float g = gla_sum_parts(parts, splits, split_stride, (int64_t)t * cols + g_col + h * P + j);
+            const int64_t at = (int64_t)t * cols + g_col + h * P + j;
+            const float g = ONE ? parts[at] : gla_sum_parts(parts, splits, split_stride, at);
             st(out + ((int64_t)t * H + h) * P + j, (row[j] * f) * w[j] * (g / (1.0f + expf(-g))));
         }
     }
@@ -452,10 +480,16 @@ WICK_API int wick_gla_mix(const float* parts, int splits, int n, int cols, int H
     if (n == 0 || n_seqs == 0) return 0;
     const int64_t stride = (int64_t)n * cols;
     // (long steps: eight tokens a block share a thread's row of W2; short ones: a block a token, for more blocks)
-    const int per_block = (n >= 512 && (size_t)rank * 8 * 4 <= 48 * 1024) ? 8 : 1;
-    WICK_CUDA(launch(gla_prepare_kernel, dim3(ceil_div(n, per_block), ceil_div(HK, GLA_PREP_THREADS) + ceil_div(HV, GLA_PREP_THREADS)),
-                     dim3(GLA_PREP_THREADS), (size_t)per_block * rank * 4, s, parts, splits, stride, cols, HK, HV, rank, w2, b2, q_scale,
-                     1.0f / tau, qkav, n, per_block));
+    const int prep_tiles = ceil_div(HK, GLA_PREP_THREADS) + ceil_div(HV, GLA_PREP_THREADS);
+    const int pb = (n >= 512 && (size_t)rank * 8 * 4 <= 16 * 1024) ? 8 : 1;
+    size_t prep_smem = (size_t)pb * rank * 4;
+    const size_t staged = (size_t)GLA_PREP_THREADS * (rank | 1) * 4;
+    const int stage = prep_smem + staged <= 48 * 1024 ? 1 : 0;          // (else a thread reads its row of W2 from memory)
+    if (stage) prep_smem += staged;
+    auto prepare = pb == 8 ? (splits == 1 ? gla_prepare_kernel<8, true> : gla_prepare_kernel<8, false>)
+                           : (splits == 1 ? gla_prepare_kernel<1, true> : gla_prepare_kernel<1, false>);
+    WICK_CUDA(launch(prepare, dim3(ceil_div(n, pb), prep_tiles), dim3(GLA_PREP_THREADS), prep_smem, s, parts, splits, stride, cols, HK, HV,
+                     rank, w2, b2, q_scale, 1.0f / tau, qkav, n, stage));
     if (check_launch("gla_prepare")) return 1;
     const int N = dk, P = dv;
     int ln = 1;
@@ -490,8 +524,9 @@ WICK_API int wick_gla_mix(const float* parts, int splits, int n, int cols, int H
         WICK_REQUIRE(H > 0 && dv > 0 && g_col >= 0 && g_col + H * dv <= cols, "gla_norm_gate: bad sizes");                     \
         if (n == 0) return 0;                                                                                                  \
         const int warps = H >= 4 ? 4 : H;                                                                                      \
-        WICK_CUDA(launch(gla_norm_gate_kernel<T>, dim3(n, ceil_div(H, warps)), dim3(32 * warps), 0, (cudaStream_t)s, y, parts, \
-                         splits, (int64_t)n * cols, cols, g_col, H, dv, w, eps, (T*)out));                                      \
+        auto kernel = splits == 1 ? gla_norm_gate_kernel<T, true> : gla_norm_gate_kernel<T, false>;                            \
+        WICK_CUDA(launch(kernel, dim3(n, ceil_div(H, warps)), dim3(32 * warps), 0, (cudaStream_t)s, y, parts, splits,          \
+                         (int64_t)n * cols, cols, g_col, H, dv, w, eps, (T*)out));                                              \
         return check_launch("gla_norm_gate");                                                                                  \
     }
 WICK_GLA_NORM_GATE(wick_gla_norm_gate_bf16, bf16)
