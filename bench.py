@@ -891,7 +891,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
-    ap.add_argument("--prefill-tokens", type=int, default=PREFILL, help="tokens of the prefill step (the contract's is 2,048)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL, help="tokens of the prefill step (the default workload's is 2,048)")
     ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of --steps decode steps each (median reported)")
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 runs")
     ap.add_argument("--skip-models", action="store_true", help="no 14b / 32b workloads")
