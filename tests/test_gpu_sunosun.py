@@ -379,7 +379,8 @@ def test_a_key_that_stands_out_far_back_and_at_page_borders(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,dk,dv,rank,tau", [(3, 8, 4, 5, 4.0), (2, 16, 16, 4, 16.0), (1, 6, 10, 3, 1.0), (2, 128, 128, 16, 8.0),
-                                               (4, 20, 36, 2, 2.0), (1, 300, 8, 7, 16.0), (2, 64, 96, 16, 16.0), (5, 9, 7, 1, 64.0)])
+                                               (4, 20, 36, 2, 2.0), (1, 300, 8, 7, 16.0), (2, 64, 96, 16, 16.0), (5, 9, 7, 1, 64.0),
+                                               (2, 16, 8, 40, 4.0), (1, 12, 20, 64, 2.0), (3, 100, 12, 33, 8.0)])
 def test_gated_linear_attention_in_any_portions(dtype, H, dk, dv, rank, tau):
     g = torch.Generator().manual_seed(H * 1000 + dk)
     width, n = 40, 350                                       # (a step of 192 tokens or more is scanned in chunks of 64)
