@@ -348,7 +348,7 @@ __device__ __forceinline__ void warp_best(float& best, int& at) {
 }
 
 __global__ void __launch_bounds__(32)
-moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int n_out, const float* __restrict__ correction,
+moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int ld, int n_out, const float* __restrict__ correction,
                   int top, int renormalize, int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ ident,
                   int scoring, int groups, int keep, float scale, float norm_eps) {
     extern __shared__ float sm[];
@@ -363,7 +363,7 @@ moe_router_kernel(const float* __restrict__ parts, int splits, int64_t split_str
     float m = -INFINITY;
     for (int e = lane; e < n_out; e += 32) {
         float z = 0.f;
-        for (int s = 0; s < splits; ++s) z += parts[s * split_stride + (int64_t)t * n_out + e];
+        for (int s = 0; s < splits; ++s) z += parts[s * split_stride + (int64_t)t * ld + e];
         score[e] = z;
         m = fmaxf(m, z);
     }
@@ -477,7 +477,8 @@ template <typename T>
 __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ row_of, const int* __restrict__ choice,
                                             const float* __restrict__ weight, const T* __restrict__ x, int n_experts, int top,
                                             float* __restrict__ out, int width, const float* __restrict__ base, int base_splits,
-                                            int64_t base_stride, const float* __restrict__ gate, int gate_splits, int64_t gate_stride) {
+                                            int64_t base_stride, const float* __restrict__ gate, int gate_splits, int64_t gate_stride,
+                                            int gate_ld) {
     pdl_trigger();
     pdl_wait();
     y = fresh(y);
@@ -491,7 +492,7 @@ __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const i
     float bf = 1.f;                                                     // the factor of what every token uses: sigmoid of the gate's number
     if (base && gate) {
         float g = 0.f;
-        for (int s = 0; s < gate_splits; ++s) g += gate[s * gate_stride + t];
+        for (int s = 0; s < gate_splits; ++s) g += gate[s * gate_stride + (int64_t)t * gate_ld];
         bf = 1.0f / (1.0f + expf(-g));
     }
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
@@ -622,19 +623,20 @@ WICK_API int wick_moe_combine(const float* y, const int* row_of, int top, float 
     return check_launch("moe_combine");
 }
 
-// parts: float32 [splits, n, n_out] (the router's logits as partial sums); correction: float32 [n_out] or null;
-// choice: int32 [n, top]; weight: float32 [n, top]; ident: int32 [n] or null.
-WICK_API int wick_moe_router(const float* parts, int splits, int n, int n_out, const float* correction, int top, int renormalize,
+// parts: float32 [splits, n, ld] (the router's logits as partial sums in a row's first n_out columns; a row may hold further
+// columns of the same product); correction: float32 [n_out] or null; choice: int32 [n, top]; weight: float32 [n, top];
+// ident: int32 [n] or null.
+WICK_API int wick_moe_router(const float* parts, int splits, int n, int ld, int n_out, const float* correction, int top, int renormalize,
                              int* choice, float* weight, int* ident, int scoring, int groups, int keep, float scale, float norm_eps,
                              void* s) {
-    WICK_REQUIRE(splits >= 1 && n_out > 0 && top > 0 && top <= n_out, "moe_router: bad sizes");
+    WICK_REQUIRE(splits >= 1 && n_out > 0 && ld >= n_out && top > 0 && top <= n_out, "moe_router: bad sizes");
     WICK_REQUIRE(scoring == 0 || scoring == 1, "moe_router: scores are a softmax (0) or sigmoids (1)");
     WICK_REQUIRE(groups == 0 || (groups > 0 && n_out % groups == 0 && keep > 0 && keep <= groups && keep * (n_out / groups) >= top),
                  "moe_router: %d outputs do not form %d equal groups of which %d hold %d choices", n_out, groups, keep, top);
     WICK_REQUIRE((size_t)(n_out + groups) * 8 <= 48 * 1024, "moe_router: %d outputs are beyond one block's shared memory", n_out);
     if (n == 0) return 0;
     WICK_CUDA(launch(moe_router_kernel, dim3(n), dim3(32), (size_t)(n_out + groups) * 2 * sizeof(float), (cudaStream_t)s, parts, splits,
-                     (int64_t)n * n_out, n_out, correction, top, renormalize, choice, weight, ident, scoring, groups, keep, scale,
+                     (int64_t)n * ld, ld, n_out, correction, top, renormalize, choice, weight, ident, scoring, groups, keep, scale,
                      norm_eps));
     return check_launch("moe_router");
 }
@@ -669,15 +671,17 @@ WICK_API int wick_moe_expert_down_f32(const void* hidden, const int* tokens, con
 // y: float32 rows; row_of: int32 [n, top] or null (rows in pair order); choice: int32 [n, top]; weight: float32 [n, top];
 // x: [n, width] or null (what an expert without matrices returns); out: float32 [n, width].
 // base: float32 [base_splits, n, width] or null: what every token uses, added with the factor sigmoid(sum of gate[:, t]) where
-// gate (float32 [gate_splits, n]) is given, else 1.
+// gate is given, else 1.  gate: a column of float32 partial sums [gate_splits, n, gate_ld], the pointer at the column's first
+// number (the gate's number may be a further column of the router's product).
 #define WICK_MOE_COMBINE_WEIGHTED(NAME, T)                                                                                    \
     WICK_API int NAME(const float* y, const int* row_of, const int* choice, const float* weight, const void* x, int n_experts, \
                       int top, float* out, int n, int width, const float* base, int base_splits, const float* gate,           \
-                      int gate_splits, void* s) {                                                                             \
+                      int gate_splits, int gate_ld, void* s) {                                                                \
         if (n == 0) return 0;                                                                                                 \
+        WICK_REQUIRE(!gate || gate_ld >= 1, "moe_combine_weighted: the gate's rows need a length");                           \
         WICK_CUDA(launch(moe_combine_weighted_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)s, y, row_of, choice, weight,     \
                          (const T*)x, n_experts, top, out, width, base, base_splits, (int64_t)n * width, gate, gate_splits,    \
-                         (int64_t)n));                                                                                         \
+                         (int64_t)n * gate_ld, gate_ld));                                                                      \
         return check_launch("moe_combine_weighted");                                                                          \
     }
 WICK_MOE_COMBINE_WEIGHTED(wick_moe_combine_weighted_bf16, bf16)

@@ -1137,9 +1137,10 @@ ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
 
 
 def moe_router(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, *, renormalize: bool = False,
-               scores: str = "softmax", groups: int = 0, keep: int = 0, scale: float = 1.0, norm_eps: float = 0.0
-               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """From the router's logits (float32 partial sums [splits, n, outputs]): scores = softmax over the outputs, or the
+               scores: str = "softmax", groups: int = 0, keep: int = 0, scale: float = 1.0, norm_eps: float = 0.0,
+               outputs: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """From the router's logits (float32 partial sums [splits, n, outputs]; with ``outputs`` a row's first ``outputs`` columns,
+    the row holding further columns of the same product): scores = softmax over the outputs, or the
     sigmoid of each (``scores``); the ``top`` outputs with the largest score + ``correction`` (float32 [outputs] or None)
     are chosen, the lowest index among equals.  ``groups`` > 0: the outputs form that many equal groups of neighbours, a
     group's score is the sum of its two largest corrected scores, and only outputs of the ``keep`` best groups can be chosen.
@@ -1149,13 +1150,15 @@ def moe_router(logits: torch.Tensor, correction: Optional[torch.Tensor], top: in
     _cuda("logits", logits, torch.float32)
     _need(logits.dim() == 3, "the router's logits come as partial sums [splits, n, outputs]")
     _need(scores in ROUTER_SCORES, f"router scores are {', '.join(ROUTER_SCORES)}, not {scores!r}")
-    splits, n, n_out = logits.shape
+    splits, n, ld = logits.shape
+    n_out = ld if outputs is None else int(outputs)
+    _need(0 < n_out <= ld, f"{n_out} outputs in rows of {ld} numbers")
     if correction is not None:
         _cuda("correction", correction, torch.float32, (n_out,))
     choice = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     ident = torch.empty((n,), dtype=torch.int32, device=logits.device)
-    _layer().call("wick_moe_router", "piiipiipppiiiffp", _p(logits), splits, n, n_out, _p(correction), int(top), 1 if renormalize else 0,
+    _layer().call("wick_moe_router", "piiiipiipppiiiffp", _p(logits), splits, n, ld, n_out, _p(correction), int(top), 1 if renormalize else 0,
                   _p(choice), _p(weight), _p(ident), ROUTER_SCORES[scores], int(groups), int(keep), float(scale), float(norm_eps),
                   _stream())
     return choice, weight, ident
@@ -1180,12 +1183,12 @@ def moe_expert_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Ten
 
 def moe_combine_weighted(y: torch.Tensor, row_of: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor,
                          x: Optional[torch.Tensor], n_experts: int, base: Optional[torch.Tensor] = None,
-                         base_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         base_gate: Optional[torch.Tensor] = None, base_gate_col: int = 0) -> torch.Tensor:
     """float32 out[t] = sum over c of weight[t, c] * r(t, c): r is row ``row_of[t, c]`` of ``y`` (row t * top + c without
     ``row_of``) where ``choice[t, c]`` < ``n_experts``, and ``x[t]`` itself where it is ``n_experts`` or more (an expert
     that returns its input; nothing if ``x`` is None).  y float32 [rows, width]; x [n, width].  ``base`` (float32 partial
     sums [splits, n, width]): what every token uses, added to the sum, times sigmoid(g_t) where ``base_gate`` (float32
-    partial sums [splits, n, 1]) gives a number g_t per token."""
+    partial sums [splits, n, cols]) gives a number g_t per token in its column ``base_gate_col``."""
     _cuda("y", y, torch.float32)
     _cuda("choice", choice, torch.int32)
     n, top = choice.shape
@@ -1197,18 +1200,20 @@ def moe_combine_weighted(y: torch.Tensor, row_of: Optional[torch.Tensor], choice
     if x is not None:
         _cuda("x", x, None, (n, width))
         dt = _dt(x)
-    bs = gs = 0
+    bs = gs = gate_ld = 0
     if base is not None:
         _cuda("base", base, torch.float32)
         _need(base.dim() == 3 and tuple(base.shape[1:]) == (n, width), f"base must be [splits, {n}, {width}]")
         bs = base.shape[0]
     if base_gate is not None:
         _cuda("base_gate", base_gate, torch.float32)
-        _need(base is not None and base_gate.dim() == 3 and tuple(base_gate.shape[1:]) == (n, 1), f"base_gate must be [splits, {n}, 1]")
-        gs = base_gate.shape[0]
+        _need(base is not None and base_gate.dim() == 3 and base_gate.shape[1] == n and 0 <= base_gate_col < base_gate.shape[2],
+              f"base_gate must be [splits, {n}, cols] with column {base_gate_col} among them")
+        gs, gate_ld = base_gate.shape[0], base_gate.shape[2]
     out = torch.empty((n, width), dtype=torch.float32, device=y.device)
-    _layer().call(f"wick_moe_combine_weighted_{dt}", "pppppiipiipipip", _p(y), _p(row_of), _p(choice), _p(weight), _p(x), int(n_experts),
-                  top, _p(out), n, width, _p(base), bs, _p(base_gate), gs, _stream())
+    gate_ptr = _p(base_gate) + 4 * int(base_gate_col) if base_gate is not None else _p(base_gate)
+    _layer().call(f"wick_moe_combine_weighted_{dt}", "pppppiipiipipiip", _p(y), _p(row_of), _p(choice), _p(weight), _p(x), int(n_experts),
+                  top, _p(out), n, width, _p(base), bs, gate_ptr, gs, gate_ld, _stream())
     return out
 
 

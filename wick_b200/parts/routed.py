@@ -84,9 +84,9 @@ class RoutedMoE(FeedForward):
         shared = p.get("shared")
         self.shared = build_part("ffn", shared, ctx) if shared is not None else None
         self.has_shared_gate = self.shared is not None and bool(p.get("shared_gate", False))
-        self.shared_gate = Linear(1, self.width, ctx) if self.has_shared_gate else None
         self.PROMPT_CAPTURABLE = self.shared is None or bool(self.shared.PROMPT_CAPTURABLE)
-        self.router = Linear(self.outputs, self.width, ctx)
+        # (the shared expert's gate is one more row of the router's matrix: one product gives the logits and the gate's number)
+        self.router = Linear(self.outputs + (1 if self.has_shared_gate else 0), self.width, ctx)
         self.correction: Optional[torch.Tensor] = None
         self.gate_up: Optional[torch.Tensor] = None      # [experts, 2, intermediate, width] (gate, up); [experts, 1, ...] for experts of one matrix
         self.down: Optional[torch.Tensor] = None         # [experts, width, intermediate]
@@ -118,12 +118,10 @@ class RoutedMoE(FeedForward):
         which = ("gate", "up") if self.gated else ("up",)
         self.gate_up = torch.stack([torch.stack([hold(fetch(self._expert(i, k)), "matrix") for k in which]) for i in range(self.experts)])
         self.down = torch.stack([hold(fetch(self._expert(i, "down")), "matrix") for i in range(self.experts)])
-        self.router.load_rows([fetch(self.names["router"])])
+        self.router.load_rows([fetch(self.names["router"])] + ([fetch(self.names["shared_gate"])] if self.has_shared_gate else []))
         self.correction = hold(fetch(self.names["correction"]), "vector") if self.has_correction else None
         if self.shared is not None:
             self.shared.load(lambda n: fetch(self.names["shared"] + n))
-        if self.has_shared_gate:
-            self.shared_gate.load_rows([fetch(self.names["shared_gate"])])
         self.up_tiles = self.down_tiles = None
         if (self.ctx.dtype == torch.bfloat16 and self.gate_up.is_cuda and not ops.plain_kernels()
                 and self.width % 8 == 0 and self.intermediate % 8 == 0):
@@ -148,7 +146,7 @@ class RoutedMoE(FeedForward):
         if self.has_correction and name == self.names["correction"]:
             return self.correction
         if self.has_shared_gate and name == self.names["shared_gate"]:
-            return self.shared_gate.rows(0, 1)
+            return self.router.rows(self.outputs, self.outputs + 1)
         if self.shared is not None and name.startswith(self.names["shared"]):
             return self.shared.tensor(name[len(self.names["shared"]):])
         return None
@@ -158,26 +156,26 @@ class RoutedMoE(FeedForward):
         el = 2 if self.ctx.dtype == torch.bfloat16 else 4
         n = self.router.weight_bytes() + min(self.top, self.experts) * (3 if self.gated else 2) * self.intermediate * self.width * el
         if self.shared is not None:
-            n += self.shared.weight_bytes() + (self.shared_gate.weight_bytes() if self.has_shared_gate else 0)
+            n += self.shared.weight_bytes()
         return n
 
     def forward(self, x, batch):
         n = x.shape[0]
-        logits = self.router.forward_delta(x)                        # float32 [splits, n, outputs]
+        logits = self.router.forward_delta(x)                        # float32 [splits, n, outputs (+ 1: the shared expert's gate)]
         choice, weight, ident = ops.moe_router(logits, self.correction, self.top, renormalize=self.renormalize, scores=self.scores,
                                                groups=self.group_count, keep=self.group_keep, scale=self.route_scale,
-                                               norm_eps=self.norm_eps)
+                                               norm_eps=self.norm_eps, outputs=self.outputs)
         own = x if self.identity else None
         base = base_gate = None
         if self.shared is not None:
             base = as_splits(self.shared.forward(x, batch))
             if self.has_shared_gate:
-                base_gate = self.shared_gate.forward_delta(x)       # float32 [splits, n, 1]
+                base_gate = logits                                  # (its last column)
         if self.up_tiles is not None and n >= self.SORTED_FROM:
             return self._forward_sorted(x, choice, weight, ident, own, base, base_gate)
         hidden = ops.moe_table_up(x, ident, choice, self.gate_up)   # [n, top, ff]; pairs of outputs without matrices are passed over
         y = ops.moe_expert_down(hidden, ident, choice, self.down)
-        return ops.moe_combine_weighted(y, None, choice, weight, own, self.experts, base, base_gate).unsqueeze(0)
+        return ops.moe_combine_weighted(y, None, choice, weight, own, self.experts, base, base_gate, self.outputs).unsqueeze(0)
 
     def _forward_sorted(self, x, choice, weight, ident, own, base=None, base_gate=None):
         from ..ops import gemm_tc
@@ -196,7 +194,7 @@ class RoutedMoE(FeedForward):
             gemm_tc.gemm_tc_pair(xs, self.up_tiles, f, out=hidden, ldo=f, b_packed=True, groups=tiles, group_rows=f_pad)
             ops.relu_squared_(hidden)
         gemm_tc.gemm_tc_pair(hidden, self.down_tiles, w, out=y, ldo=w, b_packed=True, groups=tiles, group_rows=w_pad)
-        return ops.moe_combine_weighted(y, row_of, choice, weight, own, self.experts, base, base_gate).unsqueeze(0)
+        return ops.moe_combine_weighted(y, row_of, choice, weight, own, self.experts, base, base_gate, self.outputs).unsqueeze(0)
 
 
 register_part("ffn", "routed_moe", RoutedMoE)
